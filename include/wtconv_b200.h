@@ -1,0 +1,132 @@
+/*
+ * wtconv_b200 -- C ABI of the B200 (sm_100a) WTConv forward kernels.
+ *
+ * Plain C, no torch types: raw device pointers, sizes, element strides and a
+ * CUDA stream handle passed as void*.  The library never allocates or frees
+ * device memory in the entry points below, never synchronises the stream and
+ * never throws: every call returns a status (0 = ok, <0 = rejected argument or
+ * un-built variant, >0 = a cudaError_t from the launch).  All kernels run on
+ * the CURRENT device of the calling thread, on the given stream; the entry
+ * points keep no global mutable state, so they may be called concurrently from
+ * several host threads (the reference's validate.py:263 nn.DataParallel path
+ * does that).
+ *
+ * What each entry point replaces in the reference project (paths inside the
+ * reference repository) is given beside its declaration.
+ */
+#ifndef WTCONV_B200_H_
+#define WTCONV_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* activation / parameter element types */
+#define WTCONV_F32 0
+#define WTCONV_BF16 1
+#define WTCONV_F16 2
+
+/* status codes (negative = argument errors, positive = cudaError_t) */
+#define WTCONV_OK 0
+#define WTCONV_ERR_BAD_ARG (-1)        /* null pointer, non-positive size, bad dtype code  */
+#define WTCONV_ERR_BAD_KERNEL_SIZE (-2)/* K is even or not compiled into this build         */
+#define WTCONV_ERR_BAD_LEVELS (-3)     /* wt_levels < 0 or beyond WTCONV_QUERY_MAX_LEVELS   */
+#define WTCONV_ERR_WORKSPACE (-4)      /* workspace missing or smaller than *_workspace_bytes */
+#define WTCONV_ERR_MISALIGNED (-5)     /* a pointer is not aligned to its element type      */
+#define WTCONV_ERR_TOO_LARGE (-6)      /* a dimension overflows the 32-bit index plan       */
+#define WTCONV_ERR_NO_DEVICE (-7)      /* no usable CUDA device / not an sm_100 device      */
+
+/* wtconv_query() selectors */
+#define WTCONV_QUERY_VERSION 0         /* ABI version, currently 1                          */
+#define WTCONV_QUERY_MAX_KERNEL_SIZE 1 /* largest odd K compiled in (odd K <= this work)    */
+#define WTCONV_QUERY_MAX_LEVELS 2      /* largest wt_levels accepted                        */
+#define WTCONV_QUERY_SM_ARCH 3         /* 100: built for sm_100a only                       */
+
+/* Build facts.  Mirrors the build-ceiling check of the reference's CUDA backend
+ * (fast_wtconv/cuda_haar/haar_cuda.py:65-105: MAX_KERNEL_SIZE / check_kernel_size). */
+int wtconv_query(int what);
+
+/* Human-readable text for a status returned by any entry point (static string).
+ * Counterpart of the TORCH_CHECK messages of fast_wtconv/cuda_haar/fused_haar_conv.cu:399-417. */
+const char* wtconv_status_string(int status);
+
+/* Number of floats of the packed parameter block for one layer.
+ * ndim is 2 (WTConv2d) or 1 (WTConv1d). */
+size_t wtconv_packed_param_floats(int ndim, int C, int K, int L);
+
+/*
+ * Fold a layer's parameters into the fp32 block the forward kernels read.
+ * Replaces, per call of the reference forward, the _ScaleModule multiplications
+ * (wtconv/wtconv2d.py:58,81,89-97) and the filter-bank tensors built by
+ * wtconv/util/wavelet.py:23-43: the block holds, per channel, the base taps and
+ * bias pre-multiplied by base_scale, and per level the four (two in 1-D)
+ * sub-band tap sets pre-multiplied by wavelet_scale and by the product of the
+ * analysis and synthesis taps of that depth, so the kernels run un-normalised
+ * Haar butterflies (adds only).
+ *
+ *   param_dtype      element type of every parameter pointer below
+ *   ana_tap, syn_tap magnitude of one analysis / synthesis filter tap as the
+ *                    reference module holds it (wt_filter / iwt_filter, kept in
+ *                    the module dtype: fp32 2-D taps are 0.49999997, 1-D taps
+ *                    0.70710677; a bf16 module holds 0.5 / 0.70703125)
+ *   base_w           (C,1,K,K) or (C,1,K) contiguous           base_conv.weight
+ *   base_b           (C) or NULL                               base_conv.bias
+ *   base_scale       (C)                                       base_scale.weight
+ *   wavelet_w[i]     (S*C,1,K[,K]) contiguous, S=4 (2-D) / 2   wavelet_convs[i].weight
+ *   wavelet_scale[i] (S*C)                                     wavelet_scale[i].weight
+ *   wavelet_w / wavelet_scale are HOST arrays of L device pointers.
+ *   packed           device buffer of wtconv_packed_param_floats() floats
+ * One small kernel launch on `stream`.
+ */
+int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype,
+                       double ana_tap, double syn_tap,
+                       const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale,
+                       float* packed, void* stream);
+
+/*
+ * Scratch bytes wtconv2d_forward needs for this problem (0 when the whole
+ * cascade of a plane is fused on chip, which is the case for every plane up to
+ * about 56x56; larger planes keep a coarse low-pass pyramid in scratch).
+ */
+int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, size_t* bytes);
+
+/*
+ * WTConv2d forward: y = base_scale*(base_conv(x)) + inverse-wavelet cascade of
+ * the scaled per-level sub-band depthwise convolutions, optionally subsampled
+ * by `stride`.  Replaces the whole body of WTConv2d.forward
+ * (wtconv/wtconv2d.py:38-87) including wavelet_2d_transform /
+ * inverse_2d_wavelet_transform (wtconv/util/wavelet.py:62-75); it is also the
+ * counterpart of the reference CUDA backend's fused_haar_conv_forward +
+ * ihaar_cascade + cuDNN base conv (fast_wtconv/cuda_haar/haar.cpp:5-19).
+ *
+ *   x, y        device pointers, element type `dtype`; any H,W >= 1 (odd sizes
+ *               are zero-extended in-kernel exactly like wtconv2d.py:49-51)
+ *   x_strides   4 element strides (n,c,h,w) of x; y_strides likewise for y.
+ *               NCHW-contiguous and channels-last are both native.
+ *   y shape     (B,C,ceil(H/stride),ceil(W/stride))  (wtconv2d.py:33-34,84-85)
+ *   packed      block written by wtconv_pack_params
+ *   workspace   wtconv2d_workspace_bytes() bytes of device scratch or NULL if 0
+ */
+int wtconv2d_forward(const void* x, void* y, const float* packed,
+                     void* workspace, size_t workspace_bytes,
+                     int B, int C, int H, int W, int K, int L, int stride, int dtype,
+                     const long long* x_strides, const long long* y_strides, void* stream);
+
+/*
+ * WTConv1d forward, replaces WTConv1d.forward (wtconv/wtconv1d.py:38-87) and
+ * wavelet_1d_transform / inverse_1d_wavelet_transform (wtconv/util/wavelet.py:46-59).
+ *   x (B,C,N) with 3 element strides (n,c,t); y (B,C,floor(N/stride)) --
+ *   stride>1 is a true average pool of `stride` samples (wtconv1d.py:34).
+ * The 1-D cascade is always fused on chip; no scratch memory is used.
+ */
+int wtconv1d_forward(const void* x, void* y, const float* packed,
+                     int B, int C, int N, int K, int L, int stride, int dtype,
+                     const long long* x_strides, const long long* y_strides, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WTCONV_B200_H_ */

@@ -1,0 +1,180 @@
+// TEST INFRASTRUCTURE: host emulation of the WTConv CTA bodies.
+//
+// Compiles the very same kernel bodies, planners and per-element helpers as
+// libwtconv_b200.so, but for the host: WT_PHASE becomes a loop over thread ids,
+// so one CTA is executed sequentially with the identical index arithmetic and
+// shared-memory layout.  The CPU test-suite uses it to check tiling, halos,
+// cropping and strides against the oracle without a GPU.  It is built only by
+// the tests, exports emu_* symbols only, and is never loaded by the package.
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "../../include/wtconv_b200.h"
+#include "../../wtconv_b200/csrc/wt1d_host.h"
+#include "../../wtconv_b200/csrc/wt2d_fused.cuh"
+#include "../../wtconv_b200/csrc/wt2d_host.h"
+#include "../../wtconv_b200/csrc/wt_aux.h"
+
+using namespace wt;
+
+namespace {
+
+struct AlignedBuf {
+  float* p;
+  explicit AlignedBuf(size_t floats) { p = static_cast<float*>(aligned_alloc(64, (floats * 4 + 63) / 64 * 64)); }
+  ~AlignedBuf() { free(p); }
+};
+
+template <typename T, int K>
+void run2d(const Plan2d& p, const void* x, void* y, const float* packed, const float* rin, float* rout) {
+  AlignedBuf smem(p.smem_floats + 16);
+  const long long blocks = (long long)p.ngroups * p.ntile_x * p.ntile_y * p.B;
+  for (long long b = 0; b < blocks; ++b) {
+    // poison the buffer so that a cell the kernel forgets to clear shows up
+    for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
+    wt2d_cta<T, K>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
+  }
+}
+
+template <int K>
+void run2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* packed, const float* rin, float* rout) {
+  if (dtype == 0) run2d<float, K>(p, x, y, packed, rin, rout);
+  else if (dtype == 1) run2d<__nv_bfloat16, K>(p, x, y, packed, rin, rout);
+  else run2d<__half, K>(p, x, y, packed, rin, rout);
+}
+
+template <typename T, int K>
+void run1d(const Plan1d& p, const void* x, void* y, const float* packed) {
+  AlignedBuf smem(p.smem_floats + 16);
+  const long long blocks = (long long)p.ntile * p.ngroups * p.B;
+  for (long long b = 0; b < blocks; ++b) {
+    for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
+    wt1d_cta<T, K>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, smem.p, (int)b);
+  }
+}
+
+template <int K>
+void run1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* packed) {
+  if (dtype == 0) run1d<float, K>(p, x, y, packed);
+  else if (dtype == 1) run1d<__nv_bfloat16, K>(p, x, y, packed);
+  else run1d<__half, K>(p, x, y, packed);
+}
+
+int ptr_align(const void* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  int al = 16;
+  while (al > 1 && (a % al)) al /= 2;
+  return al;
+}
+
+}  // namespace
+
+extern "C" {
+
+int emu_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                    const void* base_w, const void* base_b, const void* base_scale, const void* const* wavelet_w,
+                    const void* const* wavelet_scale, float* packed) {
+  PackArgs a;
+  a.C = C; a.L = L;
+  a.taps = (ndim == 2) ? K * K : K;
+  a.tapset = tapset_floats(K, ndim);
+  a.subbands = (ndim == 2) ? 4 : 2;
+  a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  double g = 1.0;
+  for (int l = 0; l < L; ++l) {
+    a.wavelet_w[l] = wavelet_w[l];
+    a.wavelet_scale[l] = wavelet_scale[l];
+    g *= ana_tap * syn_tap;
+    a.gain[l] = g;
+  }
+  const long long total = (long long)C * a.tapset * (1 + a.subbands * L);
+  for (long long i = 0; i < total; ++i) {
+    packed[i] = param_dtype == 0 ? pack_value<float>(a, i)
+              : param_dtype == 1 ? pack_value<__nv_bfloat16>(a, i) : pack_value<__half>(a, i);
+  }
+  return 0;
+}
+
+// Planner overrides for the following emu_* calls: edge > 0 forces the tiled
+// multi-stage path with this tile edge and `levels` levels per stage (exercises halos
+// and the stage chain on small planes); group > 0 forces the channels per CTA.
+static int g_force_edge = 0, g_force_levels = 0, g_force_group = 0;
+int emu_force(int edge, int levels, int group) {
+  g_force_edge = edge; g_force_levels = levels; g_force_group = group;
+  return 0;
+}
+
+int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int C, int H, int W, int K, int L,
+                         int stride, int dtype, const long long* xs, const long long* ys, int* info) {
+  Layer2d ly;
+  ly.B = B; ly.C = C; ly.H = H; ly.W = W; ly.K = K; ly.L = L; ly.stride = stride;
+  ly.elem_size = dtype == 0 ? 4 : 2;
+  for (int i = 0; i < 4; ++i) { ly.xs[i] = xs[i]; ly.ys[i] = ys[i]; }
+  ly.x_align = ptr_align(x);
+  ly.y_align = ptr_align(y);
+  Tuning2d tune;
+  tune.force_tiled = g_force_edge > 0;
+  tune.tile_edge = g_force_edge;
+  tune.tile_levels = g_force_levels;
+  tune.group = g_force_group;
+  Chain2d ch = plan_layer(ly, tune);
+  if (ch.status) return ch.status;
+  std::vector<float> ws((size_t)ch.scratch_floats + 4, 1.0e30f);
+  for (const Reduce2d& rd : ch.reduces) {
+    const long long total = (long long)B * C * rd.Hout * rd.Wout;
+    float* out = ws.data() + rd.out_off;
+    if (rd.in_off < 0) {
+      for (long long i = 0; i < total; ++i) {
+        out[i] = dtype == 0 ? reduce_value<float>(static_cast<const float*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3])
+               : dtype == 1 ? reduce_value<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3])
+                            : reduce_value<__half>(static_cast<const __half*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3]);
+      }
+    } else {
+      const float* in = ws.data() + rd.in_off;
+      for (long long i = 0; i < total; ++i)
+        out[i] = reduce_value<float>(in, i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift,
+                                     (long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1);
+    }
+  }
+  if (info) { info[0] = (int)ch.stages.size(); info[1] = (int)ch.reduces.size(); info[2] = ch.stages.back().plan.G; info[3] = (int)ch.stages.back().smem_bytes; }
+  for (const Stage2d& sg : ch.stages) {
+    const bool from_x = sg.xin_off < 0;
+    const void* xin = from_x ? x : static_cast<const void*>(ws.data() + sg.xin_off);
+    const float* rin = sg.rin_off < 0 ? nullptr : ws.data() + sg.rin_off;
+    float* rout = sg.rout_off < 0 ? nullptr : ws.data() + sg.rout_off;
+    const int dt = from_x ? dtype : 0;
+    switch (K) {
+      case 1: run2d_k<1>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
+      case 3: run2d_k<3>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
+      case 5: run2d_k<5>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
+      case 7: run2d_k<7>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
+      default: return WTCONV_ERR_BAD_KERNEL_SIZE;
+    }
+  }
+  return 0;
+}
+
+int emu_wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, int N, int K, int L, int stride,
+                         int dtype, const long long* xs, const long long* ys, int* info) {
+  Layer1d ly;
+  ly.B = B; ly.C = C; ly.N = N; ly.K = K; ly.L = L; ly.stride = stride;
+  for (int i = 0; i < 3; ++i) { ly.xs[i] = xs[i]; ly.ys[i] = ys[i]; }
+  if (N / stride == 0) return 0;
+  Plan1d p;
+  long long smem = 0;
+  const int st = plan_1d(p, smem, ly);
+  if (st) return st;
+  if (g_force_edge) { p.TX = g_force_edge; if (g_force_group) p.G = g_force_group; smem = layout_1d(p); }
+  if (info) { info[0] = p.ntile; info[1] = p.G; info[2] = p.TX; info[3] = (int)smem; }
+  switch (K) {
+    case 1: run1d_k<1>(p, dtype, x, y, packed); break;
+    case 3: run1d_k<3>(p, dtype, x, y, packed); break;
+    case 5: run1d_k<5>(p, dtype, x, y, packed); break;
+    case 7: run1d_k<7>(p, dtype, x, y, packed); break;
+    default: return WTCONV_ERR_BAD_KERNEL_SIZE;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,109 @@
+"""Loader of the host emulation library (TEST INFRASTRUCTURE, see tests/emu/emu.cu).
+
+Builds ``tests/emu/libwtconv_emu.so`` with nvcc (host code only) when it is
+missing or older than the kernel sources, and wraps its entry points for torch
+CPU tensors.  Nothing in the package imports this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import glob
+import os
+import subprocess
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+SRC = os.path.join(HERE, "emu", "emu.cu")
+LIB = os.path.join(HERE, "emu", "libwtconv_emu.so")
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+_lib = None
+
+
+def _stale():
+    if not os.path.exists(LIB):
+        return True
+    deps = [SRC] + glob.glob(os.path.join(ROOT, "wtconv_b200", "csrc", "*.h")) \
+        + glob.glob(os.path.join(ROOT, "wtconv_b200", "csrc", "*.cuh")) \
+        + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    t = os.path.getmtime(LIB)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False):
+    if force or _stale():
+        cmd = ["nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-fPIC", "-shared",
+               "-o", LIB, SRC]
+        subprocess.run(cmd, check=True, cwd=os.path.dirname(SRC))
+    return LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+        for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force"):
+            getattr(_lib, name).restype = ctypes.c_int
+    return _lib
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def taps(ndim, dtype):
+    """Magnitude of one analysis / synthesis tap as a reference module of `dtype` holds it."""
+    s = torch.tensor(2.0 ** -0.5, dtype=torch.float64).to(torch.float32)
+    t = (s * s) if ndim == 2 else s
+    t = t.to(dtype)
+    return float(t), float(t)
+
+
+def pack(params, ndim, C, K, L, param_dtype=torch.float32, filter_dtype=None):
+    p = {k: v.to(param_dtype).contiguous() for k, v in params.items()}
+    sub = 4 if ndim == 2 else 2
+    n = C * ((K ** ndim + 1 + 3) // 4 * 4) * (1 + sub * L)
+    packed = torch.empty(n, dtype=torch.float32)
+    ww = (ctypes.c_void_p * max(L, 1))(*[p[f"wavelet_convs.{i}.weight"].data_ptr() for i in range(L)])
+    ws = (ctypes.c_void_p * max(L, 1))(*[p[f"wavelet_scale.{i}.weight"].data_ptr() for i in range(L)])
+    ana, syn = taps(ndim, filter_dtype or param_dtype)
+    st = lib().emu_pack_params(ndim, C, K, L, DTYPE_CODE[param_dtype], ctypes.c_double(ana), ctypes.c_double(syn),
+                               _ptr(p["base_conv.weight"]), _ptr(p.get("base_conv.bias")),
+                               _ptr(p["base_scale.weight"]), ww, ws, _ptr(packed))
+    assert st == 0
+    return packed
+
+
+def forward2d(x, packed, K, L, stride=1, force=(0, 0, 0), channels_last_out=None):
+    """x: CPU tensor (B,C,H,W) in any strides; returns (y, info)."""
+    B, C, H, W = x.shape
+    Ho, Wo = -(-H // stride), -(-W // stride)
+    cl = x.stride(1) == 1 and C > 1 if channels_last_out is None else channels_last_out
+    y = torch.full((B, C, Ho, Wo), float("nan"), dtype=x.dtype)
+    if cl:
+        y = y.contiguous(memory_format=torch.channels_last)
+    xs = (ctypes.c_longlong * 4)(*x.stride())
+    ys = (ctypes.c_longlong * 4)(*y.stride())
+    info = (ctypes.c_int * 4)()
+    lib().emu_force(*force)
+    st = lib().emu_wtconv2d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, H, W, K, L, stride, DTYPE_CODE[x.dtype],
+                                    xs, ys, info)
+    lib().emu_force(0, 0, 0)
+    assert st == 0, f"emulation status {st}"
+    return y, list(info)
+
+
+def forward1d(x, packed, K, L, stride=1, force=(0, 0, 0)):
+    B, C, N = x.shape
+    y = torch.full((B, C, N // stride), float("nan"), dtype=x.dtype)
+    xs = (ctypes.c_longlong * 3)(*x.stride())
+    ys = (ctypes.c_longlong * 3)(*y.stride())
+    info = (ctypes.c_int * 4)()
+    lib().emu_force(*force)
+    st = lib().emu_wtconv1d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, N, K, L, stride, DTYPE_CODE[x.dtype],
+                                    xs, ys, info)
+    lib().emu_force(0, 0, 0)
+    assert st == 0, f"emulation status {st}"
+    return y, list(info)

@@ -1,0 +1,62 @@
+"""Kernel logic on the CPU: the CTA bodies of the CUDA kernels, compiled for the host.
+
+tests/emu/emu.cu compiles the same kernel bodies and planners as the product
+library with the phase macro turned into a loop over thread ids, so tiling,
+halos, odd-size zero extension, cropping, strides and the multi-stage chain are
+checked here against the golden vectors of the reference without a GPU.
+"""
+import numpy as np
+import pytest
+import torch
+
+import emu_lib
+from conftest import golden_names, load_golden, max_err
+
+TOL = {"float32": 1e-5, "bfloat16": 2e-2, "float16": 2e-2}
+
+
+def _params(params):
+    return {k: torch.from_numpy(v) for k, v in params.items() if "filter" not in k}
+
+
+def _run(name, layout="nchw", force=(0, 0, 0)):
+    x, params, y, meta = load_golden(name)
+    dt = getattr(torch, meta["dtype"])
+    packed = emu_lib.pack(_params(params), meta["ndim"], meta["C"], meta["K"], meta["L"],
+                          param_dtype=dt, filter_dtype=dt)
+    xt = torch.from_numpy(x).to(dt)
+    if meta["ndim"] == 2:
+        if layout == "cl":
+            xt = xt.contiguous(memory_format=torch.channels_last)
+        out, info = emu_lib.forward2d(xt, packed, meta["K"], meta["L"], meta["stride"], force)
+    else:
+        out, info = emu_lib.forward1d(xt, packed, meta["K"], meta["L"], meta["stride"], force)
+    assert tuple(out.shape) == y.shape
+    assert not torch.isnan(out.float()).any(), "kernel left output elements unwritten"
+    return max_err(out.float().numpy(), y), TOL[meta["dtype"]], info
+
+
+@pytest.mark.parametrize("layout", ["nchw", "cl"])
+@pytest.mark.parametrize("name", golden_names())
+def test_emulated_kernel_matches_reference(name, layout):
+    if name.startswith("1d") and layout == "cl":
+        pytest.skip("1-D has a single layout")
+    err, tol, _ = _run(name, layout)
+    assert err <= tol, f"{name}: err {err:.3e} > {tol}"
+
+
+@pytest.mark.parametrize("force", [(8, 1, 1), (8, 2, 2), (16, 2, 4), (16, 3, 3)])
+@pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("2d") and "1x1" not in n])
+def test_emulated_tiled_multistage_chain(name, force):
+    err, tol, info = _run(name, "cl", force)
+    assert err <= tol, f"{name} force={force}: err {err:.3e} > {tol} (stages={info[0]})"
+
+
+@pytest.mark.parametrize("force", [(64, 0, 1), (128, 0, 2)])
+@pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("1d") and "short" not in n])
+def test_emulated_1d_tiles(name, force):
+    x, params, y, meta = load_golden(name)
+    unit = (1 << meta["L"]) * 8 * meta["stride"]
+    edge = max(force[0] // unit, 1) * unit
+    err, tol, info = _run(name, "nchw", (edge, 0, force[2]))
+    assert err <= tol, f"{name}: err {err:.3e} (tiles={info[0]})"

@@ -1,0 +1,210 @@
+// extern "C" entry points of libwtconv_b200.so (see include/wtconv_b200.h).
+#include <cstdint>
+
+#include "../../include/wtconv_b200.h"
+#include "wt1d_host.h"
+#include "wt2d_host.h"
+#include "wt_aux.h"
+
+using namespace wt;
+
+namespace {
+
+inline bool valid_dtype(int d) { return d == WTCONV_F32 || d == WTCONV_BF16 || d == WTCONV_F16; }
+inline int elem_size(int d) { return d == WTCONV_F32 ? 4 : 2; }
+inline bool built_k(int K) { return K == 1 || K == 3 || K == 5 || K == 7; }
+inline int ptr_align(const void* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  int al = 16;
+  while (al > 1 && (a % al)) al /= 2;
+  return al;
+}
+
+cudaError_t launch_wt2d(const Plan2d& p, int dtype, const void* x, void* y, const float* packed, const float* rin,
+                        float* rout, size_t smem, cudaStream_t st) {
+  switch (p.K) {
+    case 1: return launch_wt2d_k<1>(p, dtype, x, y, packed, rin, rout, smem, st);
+    case 3: return launch_wt2d_k<3>(p, dtype, x, y, packed, rin, rout, smem, st);
+    case 5: return launch_wt2d_k<5>(p, dtype, x, y, packed, rin, rout, smem, st);
+    default: return launch_wt2d_k<7>(p, dtype, x, y, packed, rin, rout, smem, st);
+  }
+}
+
+cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, const float* packed, size_t smem,
+                        cudaStream_t st) {
+  switch (p.K) {
+    case 1: return launch_wt1d_k<1>(p, dtype, x, y, packed, smem, st);
+    case 3: return launch_wt1d_k<3>(p, dtype, x, y, packed, smem, st);
+    case 5: return launch_wt1d_k<5>(p, dtype, x, y, packed, smem, st);
+    default: return launch_wt1d_k<7>(p, dtype, x, y, packed, smem, st);
+  }
+}
+
+int check_common(int C, int K, int L, int dtype) {
+  if (C <= 0 || !valid_dtype(dtype)) return WTCONV_ERR_BAD_ARG;
+  if (K < 1 || (K % 2) == 0 || !built_k(K)) return WTCONV_ERR_BAD_KERNEL_SIZE;
+  if (L < 0 || L > kMaxLevels) return WTCONV_ERR_BAD_LEVELS;
+  return WTCONV_OK;
+}
+
+int make_layer2d(Layer2d& ly, const void* x, const void* y, int B, int C, int H, int W, int K, int L, int stride,
+                 int dtype, const long long* xs, const long long* ys) {
+  const int st = check_common(C, K, L, dtype);
+  if (st) return st;
+  if (B <= 0 || H <= 0 || W <= 0 || stride < 1) return WTCONV_ERR_BAD_ARG;
+  if ((long long)B * C * H * W >= (1LL << 40) || H > (1 << 24) || W > (1 << 24)) return WTCONV_ERR_TOO_LARGE;
+  ly.B = B; ly.C = C; ly.H = H; ly.W = W; ly.K = K; ly.L = L; ly.stride = stride;
+  ly.elem_size = elem_size(dtype);
+  const int Ho = cdiv(H, stride), Wo = cdiv(W, stride);
+  const long long dx[4] = {(long long)C * H * W, (long long)H * W, W, 1};
+  const long long dy[4] = {(long long)C * Ho * Wo, (long long)Ho * Wo, Wo, 1};
+  for (int i = 0; i < 4; ++i) {
+    ly.xs[i] = xs ? xs[i] : dx[i];
+    ly.ys[i] = ys ? ys[i] : dy[i];
+    if (ly.xs[i] < 0 || ly.ys[i] < 0) return WTCONV_ERR_BAD_ARG;
+  }
+  ly.x_align = ptr_align(x);
+  ly.y_align = ptr_align(y);
+  return WTCONV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int wtconv_query(int what) {
+  switch (what) {
+    case WTCONV_QUERY_VERSION: return 1;
+    case WTCONV_QUERY_MAX_KERNEL_SIZE: return kMaxK;
+    case WTCONV_QUERY_MAX_LEVELS: return kMaxLevels;
+    case WTCONV_QUERY_SM_ARCH: return 100;
+    default: return WTCONV_ERR_BAD_ARG;
+  }
+}
+
+const char* wtconv_status_string(int status) {
+  switch (status) {
+    case WTCONV_OK: return "ok";
+    case WTCONV_ERR_BAD_ARG: return "invalid argument (null pointer, non-positive size, negative stride or unknown dtype code)";
+    case WTCONV_ERR_BAD_KERNEL_SIZE: return "kernel_size must be odd and one of the sizes compiled into this build (1, 3, 5, 7)";
+    case WTCONV_ERR_BAD_LEVELS: return "wt_levels is negative or larger than this build supports";
+    case WTCONV_ERR_WORKSPACE: return "workspace pointer missing or smaller than wtconv2d_workspace_bytes()";
+    case WTCONV_ERR_MISALIGNED: return "a tensor pointer is not aligned to its element size";
+    case WTCONV_ERR_TOO_LARGE: return "problem too large for the on-chip plan (dimension or shared-memory limit)";
+    case WTCONV_ERR_NO_DEVICE: return "no usable sm_100 CUDA device";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown wtconv status";
+}
+
+size_t wtconv_packed_param_floats(int ndim, int C, int K, int L) {
+  if ((ndim != 1 && ndim != 2) || C <= 0 || K < 1 || L < 0) return 0;
+  return (size_t)C * packed_channel_floats(K, ndim, L);
+}
+
+int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                       const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale, float* packed,
+                       void* stream) {
+  if (ndim != 1 && ndim != 2) return WTCONV_ERR_BAD_ARG;
+  const int st = check_common(C, K, L, param_dtype);
+  if (st) return st;
+  if (!base_w || !base_scale || !packed || (L > 0 && (!wavelet_w || !wavelet_scale))) return WTCONV_ERR_BAD_ARG;
+  PackArgs a;
+  a.C = C; a.L = L;
+  a.taps = (ndim == 2) ? K * K : K;
+  a.tapset = tapset_floats(K, ndim);
+  a.subbands = (ndim == 2) ? 4 : 2;
+  a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  double g = 1.0;
+  for (int l = 0; l < kMaxLevels; ++l) {
+    a.wavelet_w[l] = nullptr; a.wavelet_scale[l] = nullptr; a.gain[l] = 0.0;
+  }
+  for (int l = 0; l < L; ++l) {
+    if (!wavelet_w[l] || !wavelet_scale[l]) return WTCONV_ERR_BAD_ARG;
+    a.wavelet_w[l] = wavelet_w[l];
+    a.wavelet_scale[l] = wavelet_scale[l];
+    g *= ana_tap * syn_tap;
+    a.gain[l] = g;
+  }
+  return (int)launch_pack(a, param_dtype, packed, static_cast<cudaStream_t>(stream));
+}
+
+int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, size_t* bytes) {
+  if (!bytes) return WTCONV_ERR_BAD_ARG;
+  Layer2d ly;
+  const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, nullptr, nullptr);
+  if (st) return st;
+  const Chain2d ch = plan_layer(ly);
+  if (ch.status) return ch.status;
+  *bytes = (size_t)ch.scratch_floats * sizeof(float);
+  return WTCONV_OK;
+}
+
+int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspace, size_t workspace_bytes, int B,
+                     int C, int H, int W, int K, int L, int stride, int dtype, const long long* x_strides,
+                     const long long* y_strides, void* stream) {
+  if (!x || !y || !packed) return WTCONV_ERR_BAD_ARG;
+  Layer2d ly;
+  const int st = make_layer2d(ly, x, y, B, C, H, W, K, L, stride, dtype, x_strides, y_strides);
+  if (st) return st;
+  if (ly.x_align < ly.elem_size || ly.y_align < ly.elem_size || ptr_align(packed) < 16) return WTCONV_ERR_MISALIGNED;
+  const Chain2d ch = plan_layer(ly);
+  if (ch.status) return ch.status;
+  float* ws = static_cast<float*>(workspace);
+  if (ch.scratch_floats > 0) {
+    if (!ws || workspace_bytes < (size_t)ch.scratch_floats * sizeof(float)) return WTCONV_ERR_WORKSPACE;
+    if (ptr_align(ws) < 16) return WTCONV_ERR_MISALIGNED;
+  }
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  for (const Reduce2d& rd : ch.reduces) {
+    cudaError_t e;
+    if (rd.in_off < 0) {
+      e = launch_reduce(dtype, x, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, ly.xs, cs);
+    } else {
+      const long long s[4] = {(long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1};
+      e = launch_reduce(WTCONV_F32, ws + rd.in_off, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout,
+                        rd.shift, s, cs);
+    }
+    if (e != cudaSuccess) return (int)e;
+  }
+  for (const Stage2d& sg : ch.stages) {
+    const bool from_x = sg.xin_off < 0;
+    const void* xin = from_x ? x : static_cast<const void*>(ws + sg.xin_off);
+    const float* rin = sg.rin_off < 0 ? nullptr : ws + sg.rin_off;
+    float* rout = sg.rout_off < 0 ? nullptr : ws + sg.rout_off;
+    const cudaError_t e = launch_wt2d(sg.plan, from_x ? dtype : WTCONV_F32, xin, from_x ? y : nullptr, packed, rin,
+                                      rout, (size_t)sg.smem_bytes, cs);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return WTCONV_OK;
+}
+
+int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, int N, int K, int L, int stride,
+                     int dtype, const long long* x_strides, const long long* y_strides, void* stream) {
+  if (!x || !y || !packed) return WTCONV_ERR_BAD_ARG;
+  const int st = check_common(C, K, L, dtype);
+  if (st) return st;
+  if (B <= 0 || N <= 0 || stride < 1) return WTCONV_ERR_BAD_ARG;
+  if (L > kMaxFused) return WTCONV_ERR_BAD_LEVELS;
+  if (ptr_align(x) < elem_size(dtype) || ptr_align(y) < elem_size(dtype) || ptr_align(packed) < 16)
+    return WTCONV_ERR_MISALIGNED;
+  if (N / stride == 0) return WTCONV_OK;   // empty output
+  Layer1d ly;
+  ly.B = B; ly.C = C; ly.N = N; ly.K = K; ly.L = L; ly.stride = stride;
+  const int No = N / stride;
+  const long long dx[3] = {(long long)C * N, N, 1}, dy[3] = {(long long)C * No, No, 1};
+  for (int i = 0; i < 3; ++i) {
+    ly.xs[i] = x_strides ? x_strides[i] : dx[i];
+    ly.ys[i] = y_strides ? y_strides[i] : dy[i];
+    if (ly.xs[i] < 0 || ly.ys[i] < 0) return WTCONV_ERR_BAD_ARG;
+  }
+  Plan1d p;
+  long long smem = 0;
+  const int ps = plan_1d(p, smem, ly);
+  if (ps) return ps;
+  return (int)launch_wt1d(p, dtype, x, y, packed, (size_t)smem, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

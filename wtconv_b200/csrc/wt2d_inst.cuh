@@ -1,0 +1,40 @@
+// __global__ wrapper and launcher of the fused 2-D kernel for one kernel size.
+// Each wt2d_k<K>.cu includes this file with WT_INST_K defined, so the sizes
+// compile in parallel.
+#pragma once
+
+#include "wt2d_fused.cuh"
+
+namespace wt {
+
+template <typename T, int K>
+__global__ void __launch_bounds__(256, 1)
+wt2d_fused_kernel(const __grid_constant__ Plan2d p, const T* __restrict__ x, T* __restrict__ y,
+                  const float* __restrict__ packed, const float* __restrict__ rin, float* __restrict__ rout) {
+  extern __shared__ __align__(16) float wt_smem[];
+  wt2d_cta<T, K>(p, x, y, packed, rin, rout, wt_smem, blockIdx.x);
+}
+
+template <typename T, int K>
+static cudaError_t launch_one(const Plan2d& p, const void* x, void* y, const float* packed, const float* rin,
+                              float* rout, size_t smem_bytes, cudaStream_t stream) {
+  auto kern = wt2d_fused_kernel<T, K>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (e != cudaSuccess) return e;
+  const long long blocks = (long long)p.ngroups * p.ntile_x * p.ntile_y * p.B;
+  kern<<<(unsigned)blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), static_cast<T*>(y),
+                                                             packed, rin, rout);
+  return cudaGetLastError();
+}
+
+template <int K>
+cudaError_t launch_wt2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* packed,
+                          const float* rin, float* rout, size_t smem_bytes, cudaStream_t stream) {
+  switch (dtype) {
+    case 0: return launch_one<float, K>(p, x, y, packed, rin, rout, smem_bytes, stream);
+    case 1: return launch_one<__nv_bfloat16, K>(p, x, y, packed, rin, rout, smem_bytes, stream);
+    default: return launch_one<__half, K>(p, x, y, packed, rin, rout, smem_bytes, stream);
+  }
+}
+
+}  // namespace wt

@@ -1,0 +1,118 @@
+// Launch plan and tile geometry of the fused 2-D WTConv kernel.
+//
+// One launch handles one "stage": an input plane set x (B,C,H,W), `nlev`
+// wavelet levels computed on chip, optionally the reconstruction R_in of the
+// deeper levels (fp32 planes from an earlier launch), optionally the base
+// depthwise convolution, and one output (the layer output, or fp32 planes of
+// R_0 for the next shallower launch).
+//
+// A CTA owns one (sample, channel group, output tile).  Everything a tile
+// needs is derived from the zero-extension property of the reference cascade
+// (wtconv/wtconv2d.py:49-51 pads right/bottom only and the 2x2 blocks are
+// origin aligned): treat every level as zero outside [0,H_j)x[0,W_j), then
+//   * level-j convolutions are needed on  [a_j, b_j) = tile >> j,
+//   * their inputs (sub-bands of level j) on [a_j - r, b_j + r),
+//   * the low-pass plane of level j additionally wherever level j+1 needs
+//     its 2x2 sources, i.e. on 2*need_{j+1},
+// all clipped to the plane plus a border of zeros.  With a single tile that
+// covers the plane the clipping makes every halo the constant r (= K/2), which
+// is the whole-plane-on-chip mode used for planes up to about 56x56.
+#pragma once
+
+#include "wt_common.h"
+
+namespace wt {
+
+struct Plan2d {
+  // problem of this launch
+  int B, C, H, W;
+  int K, r, rb;          // kernel size, K/2, zero border max(r,1)
+  int nlev;              // levels fused in this launch (d)
+  int lvl0;              // index of the first of them in the packed parameters
+  int has_base;          // add base conv + bias (final launch)
+  int has_rin;           // R_d is read from `rin` (fp32 planes) instead of being zero
+  int out_planes;        // output is fp32 (B,C,H,W)-contiguous planes (deep launch)
+  int out_stride;        // spatial subsampling of the output (final launch only)
+  int Hout, Wout;
+  // packed parameters
+  int wstride;           // floats per channel
+  int tapset;            // floats per tap set
+  // tiling
+  int G;                 // channels per CTA
+  int TY, TX;            // output tile (multiples of 2^nlev unless a single tile)
+  int ntile_y, ntile_x, ngroups;
+  int nthreads;
+  // per-level extents, j = 0 (input plane) .. nlev
+  int Hj[kMaxFused + 1], Wj[kMaxFused + 1];
+  int rows[kMaxFused + 1], pitch[kMaxFused + 1], off[kMaxFused + 1];
+  int rrows[kMaxFused + 1], rpitch[kMaxFused + 1], roff[kMaxFused + 1];
+  int th[kMaxFused + 1], tw[kMaxFused + 1];   // thread tile per level (j=0: base conv tile)
+  int woff;              // packed weights of the G channels
+  int smem_floats;
+  // tensor strides in elements (n,c,h,w)
+  long long xs[4], ys[4];
+  int x_cl, y_cl;        // channel is the fastest-varying dimension
+  int x_vec, y_vec;      // 16-byte channel chunks are legal for x / y
+};
+
+// Per-CTA geometry along one axis.
+struct Axis {
+  int t0, t1;                     // output range of the tile
+  int a[kMaxFused + 1];           // first position whose convolution is needed at level j
+  int n[kMaxFused + 1];           // number of such positions (b_j - a_j)
+  int lo[kMaxFused + 1];          // first position of level j that must hold data
+  int hi[kMaxFused + 1];          // one past the last such position
+  int org[kMaxFused + 1];         // position stored at array index 0
+};
+
+// Fills `ax` for the tile [t0,t1) of an axis whose level sizes are `size[j]`.
+// `vec_align` is 4 along x (window starts must be 16-byte aligned) and 1 along y.
+WT_HD void axis_geometry(int d, int r, int rb, int has_base, const int* size, int t0, int t1, int vec_align,
+                         Axis& ax) {
+  ax.t0 = t0;
+  ax.t1 = t1;
+  ax.a[0] = t0;
+  ax.n[0] = t1 - t0;
+  int lo[kMaxFused + 1], hi[kMaxFused + 1];
+  for (int j = 1; j <= d; ++j) {
+    ax.a[j] = t0 >> j;
+    ax.n[j] = ((t1 + (1 << j) - 1) >> j) - ax.a[j];
+  }
+  for (int j = d; j >= 1; --j) {
+    lo[j] = ax.a[j] - r;
+    hi[j] = ax.a[j] + ax.n[j] + r;
+    if (j < d) {
+      lo[j] = imin(lo[j], 2 * lo[j + 1]);
+      hi[j] = imax(hi[j], 2 * hi[j + 1]);
+    }
+  }
+  if (d >= 1) {
+    lo[0] = 2 * lo[1];
+    hi[0] = 2 * hi[1];
+    if (has_base) {
+      lo[0] = imin(lo[0], t0 - r);
+      hi[0] = imax(hi[0], t1 + r);
+    }
+  } else {
+    lo[0] = t0 - r;
+    hi[0] = t1 + r;
+  }
+  for (int j = 0; j <= d; ++j) {
+    ax.lo[j] = imax(lo[j], -rb);
+    ax.hi[j] = imin(hi[j], size[j] + rb);
+    // shift the origin left so that the first window (position a_j - r) lands on
+    // an index that is a multiple of vec_align
+    ax.org[j] = ax.lo[j] - pmod(ax.lo[j] - (ax.a[j] - r), vec_align);
+  }
+}
+
+// Extent (in positions) the array of level j must have along this axis: data
+// range plus the overhang of the last, partially filled thread tile.
+WT_HD int axis_extent(int r, int has_base, const Axis& ax, int j, int tile) {
+  int last = ax.hi[j];
+  const bool has_conv = (j >= 1) || has_base;
+  if (has_conv) last = imax(last, ax.a[j] + round_up(ax.n[j], tile) + r);
+  return last - ax.org[j];
+}
+
+}  // namespace wt

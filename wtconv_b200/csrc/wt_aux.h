@@ -1,0 +1,95 @@
+// Parameter folding and low-pass plane reduction: per-element bodies (shared
+// by the CUDA kernels and the host emulation used in the CPU tests) and the
+// launcher declarations used by the C-ABI translation unit.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "wt_common.h"
+
+namespace wt {
+
+struct Plan2d;
+struct Plan1d;
+
+struct PackArgs {
+  int C, L, taps, tapset, subbands;
+  const void* base_w;
+  const void* base_b;
+  const void* base_scale;
+  const void* wavelet_w[kMaxLevels];
+  const void* wavelet_scale[kMaxLevels];
+  double gain[kMaxLevels];   // (analysis tap * synthesis tap)^(level+1)
+};
+
+// Value of packed float `i`.  Layout per channel c (ts = tap-set floats):
+//   [0, ts)                      base taps * base_scale[c]; slot K^d holds bias * base_scale[c]
+//   [ts*(1 + S*l + s), +ts)      level l, sub-band s taps * wavelet_scale_l[S*c+s] * gain[l]
+// The reference applies the same factors as separate tensor ops:
+// wtconv/wtconv2d.py:58 (wavelet_scale), :81 (base_scale, bias included),
+// wtconv/util/wavelet.py:62-75 (one analysis and one synthesis tap per level).
+template <typename P>
+WT_HD float pack_value(const PackArgs& a, long long i) {
+  const int ts = a.tapset, sub = a.subbands, taps = a.taps;
+  const int per_c = ts * (1 + sub * a.L);
+  const int c = (int)(i / per_c);
+  const int rem = (int)(i - (long long)c * per_c);
+  const int set = rem / ts, k = rem - set * ts;
+  float v = 0.f;
+  if (set == 0) {
+    const float sc = Elem<P>::to_f(static_cast<const P*>(a.base_scale)[c]);
+    if (k < taps) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_w)[(size_t)c * taps + k]);
+    else if (k == taps && a.base_b) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_b)[c]);
+  } else if (k < taps) {
+    const int l = (set - 1) / sub, s = (set - 1) - l * sub;
+    const int oc = sub * c + s;
+    const float sc = Elem<P>::to_f(static_cast<const P*>(a.wavelet_scale[l])[oc]);
+    const float w = Elem<P>::to_f(static_cast<const P*>(a.wavelet_w[l])[(size_t)oc * taps + k]);
+    v = (float)((double)sc * (double)w * a.gain[l]);
+  }
+  return v;
+}
+
+// out[n][c][yo][xo] = sum of the 2^shift x 2^shift block of `in`, zero outside the
+// plane: the un-normalised low-pass plane `shift` levels further down
+// (wtconv/wtconv2d.py:49-54 applied `shift` times, taps folded into the parameters).
+template <typename T>
+WT_HD float reduce_value(const T* __restrict__ in, long long i, int C, int Hin, int Win, int Hout, int Wout,
+                         int shift, long long s0, long long s1, long long s2, long long s3) {
+  const int edge = 1 << shift;
+  const int xo = (int)(i % Wout);
+  long long t = i / Wout;
+  const int yo = (int)(t % Hout);
+  t /= Hout;
+  const int c = (int)(t % C), n = (int)(t / C);
+  const T* base = in + n * s0 + c * s1;
+  float acc = 0.f;
+  for (int dy = 0; dy < edge; ++dy) {
+    const int yy = yo * edge + dy;
+    if (yy >= Hin) break;
+    // pairwise order of the butterflies: (a+b)+(c+d) at every level
+    float racc = 0.f;
+    for (int dx = 0; dx < edge; ++dx) {
+      const int xx = xo * edge + dx;
+      if (xx >= Win) break;
+      racc += Elem<T>::to_f(base[yy * s2 + xx * s3]);
+    }
+    acc += racc;
+  }
+  return acc;
+}
+
+cudaError_t launch_pack(const PackArgs& a, int param_dtype, float* packed, cudaStream_t stream);
+
+cudaError_t launch_reduce(int dtype, const void* in, float* out, int B, int C, int Hin, int Win, int Hout,
+                          int Wout, int shift, const long long* strides, cudaStream_t stream);
+
+template <int K>
+cudaError_t launch_wt2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* packed,
+                          const float* rin, float* rout, size_t smem_bytes, cudaStream_t stream);
+
+template <int K>
+cudaError_t launch_wt1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* packed,
+                          size_t smem_bytes, cudaStream_t stream);
+
+}  // namespace wt
