@@ -1,0 +1,79 @@
+"""CPU checks of the drop-in boundary: exported symbols, module API, state_dict layout."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, golden_names, load_golden
+
+
+def _lib():
+    from wtconv_b200 import _lib as L
+    if not os.path.exists(L.LIB_PATH):
+        from wtconv_b200 import build
+        build.build()
+    return L
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib()
+    header = open(os.path.join(ROOT, "include", "wtconv_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(wtconv\w*)\s*\(", header))
+    assert declared == set(L.SYMBOLS), "header and ctypes table disagree"
+    lib = ctypes.CDLL(L.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/wtconv_b200.h but not exported"
+
+
+def test_host_only_entry_points():
+    L = _lib()
+    lib = L.load()
+    assert lib.wtconv_query(0) == 1 and lib.wtconv_query(1) == 7 and lib.wtconv_query(3) == 100
+    assert lib.wtconv_packed_param_floats(2, 96, 5, 5) == 96 * 28 * 21
+    assert lib.wtconv_packed_param_floats(1, 64, 5, 4) == 64 * 8 * 9
+    assert "odd" in L.status_string(-2)
+    nbytes = ctypes.c_size_t(123)
+    assert lib.wtconv2d_workspace_bytes(128, 96, 56, 56, 5, 5, 1, ctypes.byref(nbytes)) == 0 and nbytes.value == 0
+    assert lib.wtconv2d_workspace_bytes(2, 256, 512, 512, 5, 5, 1, ctypes.byref(nbytes)) == 0 and nbytes.value > 0
+    assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, ctypes.byref(nbytes)) == -2
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_state_dict_matches_reference_layout(name):
+    import wtconv_b200
+    x, params, y, meta = load_golden(name)
+    cls = wtconv_b200.WTConv2d if meta["ndim"] == 2 else wtconv_b200.WTConv1d
+    m = cls(meta["C"], meta["C"], kernel_size=meta["K"], stride=meta["stride"], bias=meta["bias"], wt_levels=meta["L"])
+    sd = m.state_dict()
+    assert list(sd.keys()) == list(params.keys())            # same names in the same order
+    for k, v in params.items():
+        assert tuple(sd[k].shape) == v.shape, k
+    if meta["dtype"] == "float32":
+        assert np.array_equal(sd["wt_filter"].numpy(), params["wt_filter"])
+        assert np.array_equal(sd["iwt_filter"].numpy(), params["iwt_filter"])
+    m.load_state_dict({k: torch.from_numpy(v) for k, v in params.items()}, strict=True)
+    assert not m.wt_filter.requires_grad and not m.iwt_filter.requires_grad
+    assert sum(p.numel() for p in m.parameters()) == sum(v.size for v in params.values())
+
+
+def test_module_api_and_errors():
+    import wtconv_b200
+    m = wtconv_b200.WTConv2d(8, 8, 5, 2, False, 3, 'db1')         # positional order of the reference ctor
+    assert (m.in_channels, m.wt_levels, m.stride, m.dilation) == (8, 3, 2, 1)
+    assert m.base_conv.bias is None and isinstance(m.do_stride, torch.nn.AvgPool2d)
+    with pytest.raises(AssertionError):
+        wtconv_b200.WTConv2d(8, 16)
+    with pytest.raises(NotImplementedError):
+        wtconv_b200.WTConv2d(8, 8, wt_type='db2')
+    with pytest.raises(RuntimeError, match="CUDA"):
+        with torch.no_grad():
+            m(torch.zeros(1, 8, 4, 4))
+    # substrings the reference optimiser setup keys on (wtconvnext/wtconvnext.py:372-377)
+    names = [n for n, _ in m.named_parameters()]
+    assert any("wavelet_scale" in n for n in names) and any("base_scale" in n for n in names)
+    # nn.Conv2d children are visible to the reference's _init_weights (wtconvnext/wtconvnext.py:483-487)
+    assert sum(isinstance(c, torch.nn.Conv2d) for c in m.modules()) == 4

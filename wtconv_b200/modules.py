@@ -1,0 +1,224 @@
+"""``WTConv2d`` / ``WTConv1d`` modules backed by the sm_100a kernels.
+
+Drop-in replacements for the reference layers ``wtconv/wtconv2d.py:8-87`` and
+``wtconv/wtconv1d.py:8-87``: same constructor signature and positional order,
+same sub-module / parameter names and shapes (so ``state_dict`` round-trips with
+``strict=True`` in both directions, ``wt_filter`` / ``iwt_filter`` included),
+same seeded initialisation stream.  They plug into the reference model zoo
+through its ``wtconv_class=`` hook (``wtconvnext/wtconvnext.py:76,105-114``).
+
+Only the forward pass exists, and only on CUDA: the whole cascade runs in the
+fused kernels of ``libwtconv_b200.so``; there is no PyTorch-op or CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+_SQRT_HALF = 1.0 / math.sqrt(2.0)
+# db1 taps as PyWavelets tabulates them; the reference reads them through
+# pywt.Wavelet (wtconv/util/wavelet.py:7,24) and supports nothing the table lacks.
+_DB1 = dict(dec_lo=[_SQRT_HALF, _SQRT_HALF], dec_hi=[-_SQRT_HALF, _SQRT_HALF],
+            rec_lo=[_SQRT_HALF, _SQRT_HALF], rec_hi=[_SQRT_HALF, -_SQRT_HALF])
+
+
+def _filter_bank(ndim: int, channels: int):
+    """Analysis / synthesis banks with the reference's values and shapes
+    (wtconv/util/wavelet.py:6-20 for 1-D, :23-43 for 2-D).  They are kept only for
+    ``state_dict`` compatibility; the kernels apply the Haar butterflies directly."""
+    lo_a = torch.tensor(_DB1["dec_lo"][::-1], dtype=torch.float)
+    hi_a = torch.tensor(_DB1["dec_hi"][::-1], dtype=torch.float)
+    lo_s = torch.tensor(_DB1["rec_lo"], dtype=torch.float)
+    hi_s = torch.tensor(_DB1["rec_hi"], dtype=torch.float)
+    if ndim == 1:
+        ana = torch.stack([lo_a, hi_a])[:, None].repeat(channels, 1, 1)
+        syn = torch.stack([lo_s, hi_s])[:, None].repeat(channels, 1, 1)
+        return ana, syn
+
+    def bank(lo, hi):
+        sub = [lo.unsqueeze(0) * lo.unsqueeze(1), lo.unsqueeze(0) * hi.unsqueeze(1),
+               hi.unsqueeze(0) * lo.unsqueeze(1), hi.unsqueeze(0) * hi.unsqueeze(1)]
+        return torch.stack(sub)[:, None].repeat(channels, 1, 1, 1)
+
+    return bank(lo_a, hi_a), bank(lo_s, hi_s)
+
+
+class _ScaleModule(nn.Module):
+    """Per-channel scale, same state as the reference's (wtconv/wtconv2d.py:89-97).
+    Its multiplication is folded into the packed kernel parameters."""
+
+    def __init__(self, dims, init_scale=1.0, init_bias=0):
+        super().__init__()
+        self.dims = dims
+        self.weight = nn.Parameter(torch.ones(*dims) * init_scale)
+        self.bias = None
+
+    def forward(self, x):
+        return torch.mul(self.weight, x)
+
+
+class _WTConvNd(nn.Module):
+    _ndim = 2
+
+    def __init__(self, in_channels, out_channels, kernel_size=5, stride=1, bias=True, wt_levels=1, wt_type='db1'):
+        super().__init__()
+        assert in_channels == out_channels
+        if wt_type not in ('db1', 'haar'):
+            raise NotImplementedError(f"only the db1/haar wavelet is implemented, got {wt_type!r}")
+        nd = self._ndim
+        conv = nn.Conv2d if nd == 2 else nn.Conv1d
+        sub = 4 if nd == 2 else 2
+        ones = [1] * nd
+
+        self.in_channels = in_channels
+        self.wt_levels = wt_levels
+        self.stride = stride
+        self.dilation = 1
+        self.kernel_size = kernel_size
+
+        ana, syn = _filter_bank(nd, in_channels)
+        self.wt_filter = nn.Parameter(ana, requires_grad=False)
+        self.iwt_filter = nn.Parameter(syn, requires_grad=False)
+
+        self.base_conv = conv(in_channels, in_channels, kernel_size, padding='same', stride=1, dilation=1,
+                              groups=in_channels, bias=bias)
+        self.base_scale = _ScaleModule([1, in_channels] + ones)
+        self.wavelet_convs = nn.ModuleList(
+            [conv(in_channels * sub, in_channels * sub, kernel_size, padding='same', stride=1, dilation=1,
+                  groups=in_channels * sub, bias=False) for _ in range(wt_levels)])
+        self.wavelet_scale = nn.ModuleList(
+            [_ScaleModule([1, in_channels * sub] + ones, init_scale=0.1) for _ in range(wt_levels)])
+
+        if stride > 1:   # kept for attribute parity; the kernels apply the stride themselves
+            self.do_stride = (nn.AvgPool2d(kernel_size=1, stride=stride) if nd == 2
+                              else nn.AvgPool1d(kernel_size=stride, stride=stride))
+        else:
+            self.do_stride = None
+
+        self._packed = None
+        self._packed_key = None
+        self._ws_cache = {}
+
+    # -- parameter folding -------------------------------------------------
+    def _kernel_params(self):
+        ps = [self.base_conv.weight, self.base_conv.bias, self.base_scale.weight]
+        for conv, sc in zip(self.wavelet_convs, self.wavelet_scale):
+            ps += [conv.weight, sc.weight]
+        return ps
+
+    def _packed_params(self, device):
+        """fp32 block of folded parameters, rebuilt only when a parameter changed
+        (data pointer, in-place version counter, dtype or device)."""
+        ps = self._kernel_params()
+        key = tuple((p.data_ptr(), p._version, p.dtype, p.device) if p is not None else None for p in ps) \
+            + (self.wt_filter.dtype,)
+        if self._packed is not None and key == self._packed_key and self._packed.device == device:
+            return self._packed
+        lib = _lib.load()
+        real = [p for p in ps if p is not None]
+        pdt = real[0].dtype
+        if pdt not in _DTYPE_CODE or any(p.dtype != pdt for p in real):
+            raise TypeError("WTConv parameters must share one dtype out of float32 / bfloat16 / float16")
+        if any(p.device != device for p in real):
+            raise RuntimeError("WTConv parameters and input must live on the same CUDA device")
+        nd, C, K, L = self._ndim, self.in_channels, self.kernel_size, self.wt_levels
+        # keep contiguous views alive until the launch below has been enqueued
+        hold = [p.detach().contiguous() if p is not None else None for p in ps]
+        n = lib.wtconv_packed_param_floats(nd, C, K, L)
+        packed = torch.empty(n, dtype=torch.float32, device=device)
+        # tap magnitude exactly as a reference module of this dtype stores it in
+        # wt_filter / iwt_filter (computed on the host: no device sync)
+        s = torch.tensor(_SQRT_HALF, dtype=torch.float32)
+        tap = float(((s * s) if nd == 2 else s).to(self.wt_filter.dtype))
+        arr_t = ctypes.c_void_p * max(L, 1)
+        ww = arr_t(*[hold[3 + 2 * i].data_ptr() for i in range(L)])
+        ws = arr_t(*[hold[4 + 2 * i].data_ptr() for i in range(L)])
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            st = lib.wtconv_pack_params(nd, C, K, L, _DTYPE_CODE[pdt], tap, tap,
+                                        hold[0].data_ptr(), hold[1].data_ptr() if hold[1] is not None else None,
+                                        hold[2].data_ptr(), ww, ws, packed.data_ptr(), stream)
+        _lib.check(st, "wtconv_pack_params")
+        self._packed, self._packed_key = packed, key
+        return packed
+
+    def _check_input(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("wtconv_b200 layers run only on CUDA tensors (sm_100a kernels, no CPU path)")
+        if x.dtype not in _DTYPE_CODE:
+            raise TypeError(f"unsupported activation dtype {x.dtype}; use float32, bfloat16 or float16")
+        if x.dim() != self._ndim + 2 or x.shape[1] != self.in_channels:
+            raise ValueError(f"expected a {self._ndim + 2}-D input with {self.in_channels} channels, got {tuple(x.shape)}")
+        if torch.is_grad_enabled() and (x.requires_grad or any(
+                p is not None and p.requires_grad for p in self._kernel_params())):
+            raise NotImplementedError(
+                "wtconv_b200 implements the forward pass only: call it under torch.no_grad() / "
+                "torch.inference_mode() (no autograd graph is recorded)")
+
+
+class WTConv2d(_WTConvNd):
+    """Wavelet convolution layer, forward on B200 (reference: wtconv/wtconv2d.py:8-87)."""
+    _ndim = 2
+
+    def forward(self, x):
+        self._check_input(x)
+        lib = _lib.load()
+        B, C, H, W = x.shape
+        s = self.stride
+        if x.numel() == 0:
+            return x.new_empty((B, C, -(-H // s), -(-W // s)))
+        channels_last = x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()
+        if not channels_last and not x.is_contiguous():
+            x = x.contiguous()
+        y = torch.empty((B, C, -(-H // s), -(-W // s)), dtype=x.dtype, device=x.device,
+                        memory_format=torch.channels_last if channels_last else torch.contiguous_format)
+        packed = self._packed_params(x.device)
+        K, L, code = self.kernel_size, self.wt_levels, _DTYPE_CODE[x.dtype]
+        key = (B, C, H, W, code)
+        nbytes = self._ws_cache.get(key)
+        if nbytes is None:
+            out = ctypes.c_size_t(0)
+            _lib.check(lib.wtconv2d_workspace_bytes(B, C, H, W, K, L, code, ctypes.byref(out)),
+                       "wtconv2d_workspace_bytes")
+            nbytes = self._ws_cache[key] = int(out.value)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
+        xs = (ctypes.c_longlong * 4)(*x.stride())
+        ys = (ctypes.c_longlong * 4)(*y.stride())
+        with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+            st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
+                                      ws.data_ptr() if ws is not None else None, nbytes,
+                                      B, C, H, W, K, L, s, code, xs, ys, stream)
+        _lib.check(st, "wtconv2d_forward")
+        return y
+
+
+class WTConv1d(_WTConvNd):
+    """1-D wavelet convolution layer, forward on B200 (reference: wtconv/wtconv1d.py:8-87)."""
+    _ndim = 1
+
+    def forward(self, x):
+        self._check_input(x)
+        lib = _lib.load()
+        B, C, N = x.shape
+        s = self.stride
+        y = torch.empty((B, C, N // s), dtype=x.dtype, device=x.device)
+        if y.numel() == 0:
+            return y
+        if x.stride(2) != 1:
+            x = x.contiguous()
+        packed = self._packed_params(x.device)
+        xs = (ctypes.c_longlong * 3)(*x.stride())
+        ys = (ctypes.c_longlong * 3)(*y.stride())
+        with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+            st = lib.wtconv1d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(), B, C, N, self.kernel_size,
+                                      self.wt_levels, s, _DTYPE_CODE[x.dtype], xs, ys, stream)
+        _lib.check(st, "wtconv1d_forward")
+        return y
