@@ -98,10 +98,11 @@ int emu_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_t
 
 // Planner overrides for the following emu_* calls: edge > 0 forces the tiled
 // multi-stage path with this tile edge and `levels` levels per stage (exercises halos
-// and the stage chain on small planes); group > 0 forces the channels per CTA.
-static int g_force_edge = 0, g_force_levels = 0, g_force_group = 0;
-int emu_force(int edge, int levels, int group) {
-  g_force_edge = edge; g_force_levels = levels; g_force_group = group;
+// and the stage chain on small planes); group > 0 forces the channels per CTA; mode 2 tiles
+// every stage, which makes chains of three and more stages with materialised low-pass planes.
+static int g_force_edge = 0, g_force_levels = 0, g_force_group = 0, g_force_mode = 1;
+int emu_force(int edge, int levels, int group, int mode) {
+  g_force_edge = edge; g_force_levels = levels; g_force_group = group; g_force_mode = mode ? mode : 1;
   return 0;
 }
 
@@ -114,8 +115,9 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
   ly.x_align = ptr_align(x);
   ly.y_align = ptr_align(y);
   Tuning2d tune;
-  tune.force_tiled = g_force_edge > 0;
-  tune.tile_edge = g_force_edge;
+  tune.force_tiled = g_force_edge > 0 ? g_force_mode : 0;
+  tune.tile_y = g_force_edge;
+  tune.tile_x = g_force_edge;
   tune.tile_levels = g_force_levels;
   tune.group = g_force_group;
   Chain2d ch = plan_layer(ly, tune);
@@ -140,15 +142,16 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
   if (info) { info[0] = (int)ch.stages.size(); info[1] = (int)ch.reduces.size(); info[2] = ch.stages.back().plan.G; info[3] = (int)ch.stages.back().smem_bytes; }
   for (const Stage2d& sg : ch.stages) {
     const bool from_x = sg.xin_off < 0;
+    const bool final_stage = sg.rout_off < 0;
     const void* xin = from_x ? x : static_cast<const void*>(ws.data() + sg.xin_off);
     const float* rin = sg.rin_off < 0 ? nullptr : ws.data() + sg.rin_off;
-    float* rout = sg.rout_off < 0 ? nullptr : ws.data() + sg.rout_off;
+    float* rout = final_stage ? nullptr : ws.data() + sg.rout_off;
     const int dt = from_x ? dtype : 0;
     switch (K) {
-      case 1: run2d_k<1>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
-      case 3: run2d_k<3>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
-      case 5: run2d_k<5>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
-      case 7: run2d_k<7>(sg.plan, dt, xin, from_x ? y : nullptr, packed, rin, rout); break;
+      case 1: run2d_k<1>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
+      case 3: run2d_k<3>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
+      case 5: run2d_k<5>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
+      case 7: run2d_k<7>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
       default: return WTCONV_ERR_BAD_KERNEL_SIZE;
     }
   }

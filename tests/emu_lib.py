@@ -87,10 +87,10 @@ def forward2d(x, packed, K, L, stride=1, force=(0, 0, 0), channels_last_out=None
     xs = (ctypes.c_longlong * 4)(*x.stride())
     ys = (ctypes.c_longlong * 4)(*y.stride())
     info = (ctypes.c_int * 4)()
-    lib().emu_force(*force)
+    lib().emu_force(*(tuple(force) + (0,) * (4 - len(force))))
     st = lib().emu_wtconv2d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, H, W, K, L, stride, DTYPE_CODE[x.dtype],
                                     xs, ys, info)
-    lib().emu_force(0, 0, 0)
+    lib().emu_force(0, 0, 0, 0)
     assert st == 0, f"emulation status {st}"
     return y, list(info)
 
@@ -101,9 +101,9 @@ def forward1d(x, packed, K, L, stride=1, force=(0, 0, 0)):
     xs = (ctypes.c_longlong * 3)(*x.stride())
     ys = (ctypes.c_longlong * 3)(*y.stride())
     info = (ctypes.c_int * 4)()
-    lib().emu_force(*force)
+    lib().emu_force(*(tuple(force) + (0,) * (4 - len(force))))
     st = lib().emu_wtconv1d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, N, K, L, stride, DTYPE_CODE[x.dtype],
                                     xs, ys, info)
-    lib().emu_force(0, 0, 0)
+    lib().emu_force(0, 0, 0, 0)
     assert st == 0, f"emulation status {st}"
     return y, list(info)

@@ -45,11 +45,13 @@ def test_emulated_kernel_matches_reference(name, layout):
     assert err <= tol, f"{name}: err {err:.3e} > {tol}"
 
 
-@pytest.mark.parametrize("force", [(8, 1, 1), (8, 2, 2), (16, 2, 4), (16, 3, 3)])
+@pytest.mark.parametrize("force", [(8, 1, 1), (8, 2, 2), (16, 2, 4), (16, 3, 3), (8, 1, 2, 2), (16, 2, 1, 2)])
 @pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("2d") and "1x1" not in n])
 def test_emulated_tiled_multistage_chain(name, force):
     err, tol, info = _run(name, "cl", force)
     assert err <= tol, f"{name} force={force}: err {err:.3e} > {tol} (stages={info[0]})"
+    if len(force) == 4 and force[3] == 2 and name == "2d_c8_k5_l5_56":
+        assert info[0] >= 3 and info[1] >= 2      # chain with materialised low-pass planes
 
 
 @pytest.mark.parametrize("force", [(64, 0, 1), (128, 0, 2)])

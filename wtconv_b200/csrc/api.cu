@@ -1,5 +1,7 @@
 // extern "C" entry points of libwtconv_b200.so (see include/wtconv_b200.h).
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 
 #include "../../include/wtconv_b200.h"
 #include "wt1d_host.h"
@@ -38,6 +40,21 @@ cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, cons
     case 5: return launch_wt1d_k<5>(p, dtype, x, y, packed, smem, st);
     default: return launch_wt1d_k<7>(p, dtype, x, y, packed, smem, st);
   }
+}
+
+// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group"
+// (integers, 0 = automatic).  Read once; absent in normal use.
+const Tuning2d& env_tuning() {
+  static const Tuning2d t = [] {
+    Tuning2d v;
+    if (const char* e = getenv("WTCONV_TUNE")) {
+      int a = 0, b = 0, c = 0, d = 0, g = 0;
+      sscanf(e, "%d,%d,%d,%d,%d", &a, &b, &c, &d, &g);
+      v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g;
+    }
+    return v;
+  }();
+  return t;
 }
 
 int check_common(int C, int K, int L, int dtype) {
@@ -136,7 +153,7 @@ int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype
   Layer2d ly;
   const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, nullptr, nullptr);
   if (st) return st;
-  const Chain2d ch = plan_layer(ly);
+  const Chain2d ch = plan_layer(ly, env_tuning());
   if (ch.status) return ch.status;
   *bytes = (size_t)ch.scratch_floats * sizeof(float);
   return WTCONV_OK;
@@ -150,7 +167,7 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
   const int st = make_layer2d(ly, x, y, B, C, H, W, K, L, stride, dtype, x_strides, y_strides);
   if (st) return st;
   if (ly.x_align < ly.elem_size || ly.y_align < ly.elem_size || ptr_align(packed) < 16) return WTCONV_ERR_MISALIGNED;
-  const Chain2d ch = plan_layer(ly);
+  const Chain2d ch = plan_layer(ly, env_tuning());
   if (ch.status) return ch.status;
   float* ws = static_cast<float*>(workspace);
   if (ch.scratch_floats > 0) {
@@ -170,12 +187,13 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     if (e != cudaSuccess) return (int)e;
   }
   for (const Stage2d& sg : ch.stages) {
-    const bool from_x = sg.xin_off < 0;
+    const bool from_x = sg.xin_off < 0;          // the layer input (directly, or reduced while loading)
+    const bool final_stage = sg.rout_off < 0;
     const void* xin = from_x ? x : static_cast<const void*>(ws + sg.xin_off);
     const float* rin = sg.rin_off < 0 ? nullptr : ws + sg.rin_off;
-    float* rout = sg.rout_off < 0 ? nullptr : ws + sg.rout_off;
-    const cudaError_t e = launch_wt2d(sg.plan, from_x ? dtype : WTCONV_F32, xin, from_x ? y : nullptr, packed, rin,
-                                      rout, (size_t)sg.smem_bytes, cs);
+    float* rout = final_stage ? nullptr : ws + sg.rout_off;
+    const cudaError_t e = launch_wt2d(sg.plan, from_x ? dtype : WTCONV_F32, xin, final_stage ? y : nullptr, packed,
+                                      rin, rout, (size_t)sg.smem_bytes, cs);
     if (e != cudaSuccess) return (int)e;
   }
   return WTCONV_OK;

@@ -14,7 +14,6 @@ constexpr int kSmemLimitBytes = 232448;    // 227 KB opt-in dynamic shared memor
 constexpr int kSmemTwoPerSm = 113 * 1024;  // budget that lets two CTAs share one SM
 constexpr int kThreads2d = 256;
 constexpr int kTiledLevels = 2;            // levels fused per stage when a plane has to be tiled
-constexpr int kTiledEdge = 64;             // output tile edge of a tiled stage
 
 // thread-tile height for `n` rows out of a menu (largest first): cheapest padded
 // row count, with a small penalty for short tiles (they reuse fewer loaded rows)
@@ -37,7 +36,6 @@ inline long long layout_stage(Plan2d& p) {
   p.r = p.K / 2;
   p.rb = imax(p.r, 1);
   p.tapset = tapset_floats(p.K, 2);
-  p.nthreads = kThreads2d;
   p.Hj[0] = p.H;
   p.Wj[0] = p.W;
   for (int j = 1; j <= d; ++j) {
@@ -48,17 +46,18 @@ inline long long layout_stage(Plan2d& p) {
   p.ntile_x = cdiv(p.W, p.TX);
   p.ngroups = cdiv(p.C, p.G);
 
-  static const int lvl_menu[3] = {4, 2, 1};
-  static const int base_menu[3] = {8, 4, 2};
+  // thread tiles: the top level runs 2x4-position items (fused with a 4x8-pixel base
+  // tile); deeper levels run one sub-band of a 4x4 or 2x4 tile per item
+  static const int deep_menu[2] = {4, 2};
   const int ny0 = imin(p.TY, p.H);
   for (int j = 0; j <= d; ++j) {
     const int nyj = (ny0 + (1 << j) - 1) >> j;
-    p.th[j] = (j == 0) ? pick_tile(nyj, base_menu, 3, 0.10) : pick_tile(nyj, lvl_menu, 3, 0.15);
-    p.tw[j] = 4;
+    p.th[j] = (j == 0) ? 4 : (j == 1) ? 2 : pick_tile(nyj, deep_menu, 2, 0.15);
+    p.tw[j] = (j == 0) ? 8 : 4;
   }
 
   // static extents = maximum over all tiles of the per-CTA extents
-  int ext[2][kMaxFused + 1], rext[2][kMaxFused + 1];
+  int ext[2][kMaxFused + 1], rext[2][kMaxFused + 1], yext[2] = {0, 0};
   for (int a = 0; a < 2; ++a)
     for (int j = 0; j <= kMaxFused; ++j) ext[a][j] = rext[a][j] = 0;
   for (int axis = 0; axis < 2; ++axis) {
@@ -67,35 +66,59 @@ inline long long layout_stage(Plan2d& p) {
     const int size0 = axis ? p.W : p.H;
     const int* sizes = axis ? p.Wj : p.Hj;
     for (int t = 0; t < ntile; ++t) {
+      if (t >= 2 && t < ntile - 2) continue;   // interior tiles are all alike
       Axis ax;
       axis_geometry(d, p.r, p.rb, p.has_base, sizes, t * T, imin(size0, (t + 1) * T), axis ? 4 : 1, ax);
       for (int j = 0; j <= d; ++j) {
         const int tile = axis ? p.tw[j] : p.th[j];
         ext[axis][j] = imax(ext[axis][j], axis_extent(p.r, p.has_base, ax, j, tile));
-        const bool tiled = (j >= 1) || p.has_base;
-        rext[axis][j] = imax(rext[axis][j], tiled ? round_up(ax.n[j], tile) : ax.n[j]);
+        // R_1 is read by whole top-level items, R_0 (deep stages only) and R_j, j>=2 element-wise
+        rext[axis][j] = imax(rext[axis][j], (j == 1) ? round_up(ax.n[j], tile) : ax.n[j]);
+        if (j >= 2) yext[axis] = imax(yext[axis], round_up(ax.n[j], tile));
       }
     }
   }
   long long off = 0;
   p.woff = (int)off;
-  off += (long long)p.G * p.wstride;
+  p.wsm = p.tapset * (p.has_base + 4 * d);
+  off += (long long)p.G * p.wsm;
   for (int j = 0; j <= d; ++j) {
     p.rows[j] = ext[0][j];
     p.pitch[j] = round_up(ext[1][j], 4);
     p.off[j] = (int)off;
     off += (long long)p.G * (j == 0 ? 1 : 4) * p.rows[j] * p.pitch[j];
   }
+  p.yrows = yext[0];
+  p.ypitch = round_up(yext[1], 4);
+  p.yoff = (int)off;
+  off += (long long)p.G * 4 * p.yrows * p.ypitch;
   for (int j = 0; j <= d; ++j) {
-    const bool needed = (j < d) || (j == 0) || p.has_rin;
+    // R_0 only exists in stages without a base convolution (their output); R_d only when
+    // an earlier launch provides it
+    const bool needed = (j == 0) ? !p.has_base : ((j < d) || p.has_rin);
     p.rrows[j] = needed ? rext[0][j] : 0;
     p.rpitch[j] = needed ? round_up(rext[1][j], 4) : 0;
     p.roff[j] = (int)off;
     off += (long long)p.G * p.rrows[j] * p.rpitch[j];
   }
+  p.ooff = (int)off;
+  p.orows = p.opitch = 0;
+  if (p.has_base) {
+    const int tile_y = imin(p.TY, p.H), tile_x = imin(p.TX, p.W);
+    p.orows = round_up(tile_y, 4);
+    p.opitch = round_up(tile_x, 8);
+    off += ((long long)p.G * p.orows * p.opitch * p.elem_size + 3) / 4;
+  }
   off += 4;                       // the last window may over-read up to three floats
   off = (off + 3) / 4 * 4;
   p.smem_floats = (int)off;
+  // threads: enough for one top-level item each, at least four warps
+  {
+    const int tile_y = imin(p.TY, p.H), tile_x = imin(p.TX, p.W);
+    const int items = (d >= 1) ? p.G * cdiv((tile_y + 1) / 2, 2) * cdiv((tile_x + 1) / 2, 4)
+                               : p.G * cdiv(tile_y, 4) * cdiv(tile_x, 8);
+    p.nthreads = items > 160 ? 256 : 128;
+  }
   return off * 4;
 }
 
@@ -141,9 +164,10 @@ inline int vec_bytes(const long long* s, int G, int elem_size, int ptr_align) {
   return 0;
 }
 
-// Plan one stage with a fixed tiling; returns smem bytes
+// Plan one stage with a fixed tiling; returns smem bytes.  `in_shift` > 0: the stage reads
+// the layer input and forms its low-pass plane of level `first_level` while loading.
 inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int first_level, int nlev,
-                            bool final_stage, bool has_rin, int G, int TY, int TX) {
+                            bool final_stage, bool has_rin, int G, int TY, int TX, int in_shift = 0) {
   p = Plan2d();
   p.B = ly.B; p.C = ly.C; p.H = H; p.W = W; p.K = ly.K;
   p.nlev = nlev;
@@ -155,8 +179,13 @@ inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int firs
   p.Hout = final_stage ? cdiv(H, ly.stride) : H;
   p.Wout = final_stage ? cdiv(W, ly.stride) : W;
   p.wstride = packed_channel_floats(ly.K, 2, ly.L);
+  p.in_shift = in_shift;
+  p.Hsrc = in_shift ? ly.H : H;
+  p.Wsrc = in_shift ? ly.W : W;
+  const bool from_x = (first_level == 0) || in_shift > 0;
+  p.elem_size = from_x ? ly.elem_size : 4;
   p.G = G; p.TY = TY; p.TX = TX;
-  if (first_level == 0) {
+  if (from_x) {
     for (int i = 0; i < 4; ++i) p.xs[i] = ly.xs[i];
     p.x_cl = (ly.xs[1] == 1 && ly.C > 1) ? 1 : 0;
     p.x_vec = vec_bytes(ly.xs, G, ly.elem_size, ly.x_align);
@@ -172,111 +201,134 @@ inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int firs
   return layout_stage(p);
 }
 
-// Whole-plane stage: single tile, all `nlev` levels on chip.  Picks G; returns false if
-// even one channel does not fit.
-inline bool plan_whole_plane(Plan2d& p, long long& smem, const Layer2d& ly, int H, int W, int first_level,
-                             int nlev, bool final_stage, int forced_group = 0) {
+// Optional planner overrides (all zero = automatic).  Used by tuning sweeps and by
+// the tests to exercise the tiled multi-stage path on small planes.
+struct Tuning2d {
+  int force_tiled = 0;   // 1: never use the whole-plane mode for the top stage; 2: for no stage
+  int tile_y = 0;        // output tile of tiled stages
+  int tile_x = 0;
+  int tile_levels = 0;   // levels fused per tiled stage
+  int group = 0;         // channels per CTA
+};
+
+// Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
+// group that lets two CTAs share an SM (or the forced one).  `good` tells whether that
+// group still moves at least 8 bytes per pixel of a channels-last tensor.
+inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer2d& ly, int H, int W,
+                             int first_level, int nlev, bool final_stage, int in_shift, int forced_group = 0) {
+  good = false;
   if (nlev > kMaxFused) return false;
+  const int TY = imax(H, 1), TX = imax(W, 1);
   if (forced_group > 0) {
-    smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, forced_group, imax(H, 1), imax(W, 1));
-    return smem <= kSmemLimitBytes;
+    smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, forced_group, TY, TX, in_shift);
+    good = smem <= kSmemLimitBytes;
+    return good;
   }
   static const int cand[5] = {16, 8, 4, 2, 1};
-  const int TY = imax(H, 1), TX = imax(W, 1);
   int fit_two = 0, fit_one = 0;
   for (int i = 0; i < 5; ++i) {
     const int G = cand[i];
     if (G > ly.C && G != 1) continue;
     Plan2d q;
-    const long long bytes = plan_stage(q, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX);
+    const long long bytes = plan_stage(q, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX, in_shift);
     if (!fit_two && bytes <= kSmemTwoPerSm) fit_two = G;
     if (!fit_one && bytes <= kSmemLimitBytes) fit_one = G;
   }
-  int G = 0;
-  if (fit_two >= 4) G = fit_two;
-  else if (fit_one) G = imin(fit_one, 4) > fit_two ? imin(fit_one, 4) : fit_two;
+  const int G = fit_two ? fit_two : fit_one;
   if (G == 0) return false;
-  smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX);
-  if (smem > kSmemLimitBytes) {   // imin(fit_one,4) is a candidate that fits by construction
-    return false;
-  }
+  smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX, in_shift);
+  const bool from_x = (first_level == 0) || in_shift > 0;
+  const bool channels_last = from_x && ly.xs[1] == 1 && ly.C > 1;
+  good = fit_two > 0 && (!channels_last || G * ly.elem_size >= 8 || G >= ly.C);
   return true;
 }
-
-// Optional planner overrides (all zero = automatic).  Used by tuning sweeps and by
-// the tests to exercise the tiled multi-stage path on small planes.
-struct Tuning2d {
-  int force_tiled = 0;   // never use the whole-plane mode
-  int tile_edge = 0;     // output tile edge of tiled stages
-  int tile_levels = 0;   // levels fused per tiled stage
-  int group = 0;         // channels per CTA
-};
 
 // Builds the launch chain of one layer.
 inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) {
   Chain2d ch;
-  const int tiled_levels = tune.tile_levels > 0 ? imin(tune.tile_levels, kMaxFused) : kTiledLevels;
-  const int tiled_edge = tune.tile_edge > 0 ? round_up(tune.tile_edge, 1 << tiled_levels) : kTiledEdge;
   // level sizes of the whole pyramid
   std::vector<int> Hl(ly.L + 1), Wl(ly.L + 1);
   Hl[0] = ly.H; Wl[0] = ly.W;
   for (int j = 1; j <= ly.L; ++j) { Hl[j] = (Hl[j - 1] + 1) / 2; Wl[j] = (Wl[j - 1] + 1) / 2; }
 
-  // top-down: decide the stage boundaries
+  // top-down: decide the stage boundaries.  A stage is "whole" (its plane and every
+  // deeper level stay on chip) or "tiled" (a few levels on halo tiles, the rest below).
   struct Cut { int first, nlev; bool whole; };
   std::vector<Cut> cuts;
   int q = 0;
   while (true) {
     const int remaining = ly.L - q;
-    Plan2d tmp; long long bytes = 0;
-    if (!tune.force_tiled && remaining <= kMaxFused &&
-        plan_whole_plane(tmp, bytes, ly, Hl[q], Wl[q], q, remaining, q == 0, tune.group)) {
+    Plan2d tmp; long long bytes = 0; bool good = false;
+    const bool fits = !(tune.force_tiled == 2 && remaining > 0) && !(tune.force_tiled && q == 0) &&
+                      remaining <= kMaxFused &&
+                      plan_whole_plane(tmp, bytes, good, ly, Hl[q], Wl[q], q, remaining, q == 0, 0, tune.group);
+    // a deep stage (q > 0) that fits is always taken; the top stage only if it is efficient
+    if (fits && (good || q > 0 || remaining == 0)) {
       cuts.push_back({q, remaining, true});
       break;
     }
-    const int nlev = imin(remaining, tiled_levels);
+    int nlev = tune.tile_levels > 0 ? imin(tune.tile_levels, kMaxFused)
+                                    : ((Hl[q] > 128 || Wl[q] > 128) ? kTiledLevels : 1);
+    nlev = imin(remaining, nlev);
+    if (fits && nlev == remaining) {   // nothing to split off below: keep the whole-plane stage
+      cuts.push_back({q, remaining, true});
+      break;
+    }
     cuts.push_back({q, nlev, false});
     q += nlev;
     if (q == ly.L) break;   // also ends a base-only layer (nlev == 0)
   }
-  // scratch: for every cut after the first, low-pass planes of its input level and
-  // the reconstruction it hands up
+  // With exactly one deep stage it reads the layer input itself and forms its low-pass
+  // plane while loading; with more, the low-pass planes are materialised in scratch.
+  const bool direct = (cuts.size() == 2);
   long long off = 0;
   std::vector<long long> xoff(cuts.size(), -1), roff(cuts.size(), -1);
   for (size_t i = 1; i < cuts.size(); ++i) {
     const long long n = (long long)ly.B * ly.C * Hl[cuts[i].first] * Wl[cuts[i].first];
-    xoff[i] = off; off += (n + 3) / 4 * 4;
+    if (!direct) { xoff[i] = off; off += (n + 3) / 4 * 4; }
     roff[i] = off; off += (n + 3) / 4 * 4;
   }
   ch.scratch_floats = off;
-  for (size_t i = 1; i < cuts.size(); ++i) {
-    Reduce2d rd;
-    const int from = cuts[i - 1].first, to = cuts[i].first;
-    rd.in_off = xoff[i - 1];
-    rd.out_off = xoff[i];
-    rd.Hin = Hl[from]; rd.Win = Wl[from]; rd.Hout = Hl[to]; rd.Wout = Wl[to];
-    rd.shift = to - from;
-    ch.reduces.push_back(rd);
+  if (!direct) {
+    for (size_t i = 1; i < cuts.size(); ++i) {
+      Reduce2d rd;
+      const int from = cuts[i - 1].first, to = cuts[i].first;
+      rd.in_off = xoff[i - 1];
+      rd.out_off = xoff[i];
+      rd.Hin = Hl[from]; rd.Win = Wl[from]; rd.Hout = Hl[to]; rd.Wout = Wl[to];
+      rd.shift = to - from;
+      ch.reduces.push_back(rd);
+    }
   }
   for (int i = (int)cuts.size() - 1; i >= 0; --i) {
     Stage2d st;
     const Cut& c = cuts[i];
     const bool final_stage = (c.first == 0);
     const bool has_rin = (i + 1 < (int)cuts.size());
+    const int in_shift = (direct && i == 1) ? c.first : 0;
+    const int H = Hl[c.first], W = Wl[c.first];
     if (c.whole) {
-      if (!plan_whole_plane(st.plan, st.smem_bytes, ly, Hl[c.first], Wl[c.first], c.first, c.nlev, final_stage,
-                            tune.group)) {
+      bool good = false;
+      if (!plan_whole_plane(st.plan, st.smem_bytes, good, ly, H, W, c.first, c.nlev, final_stage, in_shift,
+                            final_stage ? tune.group : 0)) {
         ch.status = -6; return ch;
       }
     } else {
+      // tile: a band across the plane when it is narrow, else a square; the channel group is
+      // one 16-byte chunk of a channels-last tensor
+      const bool from_x = final_stage || in_shift > 0;
+      const int unit = 1 << (c.nlev + 1);                  // tiles start on top-item boundaries
+      int TX = tune.tile_x > 0 ? tune.tile_x : (W <= 64 ? W : 64);
+      int TY = tune.tile_y > 0 ? tune.tile_y : (W <= 64 ? 16 : 32);
+      TY = round_up(TY, unit);
+      if (TX < W) TX = round_up(TX, imax(unit, 8));
       int G = 4;
-      const int cb_chunk = (ly.elem_size == 2) ? 8 : 4;
-      if (final_stage && ly.xs[1] == 1 && ly.C % cb_chunk == 0) G = cb_chunk;
+      const int chunk = 16 / ly.elem_size;
+      if (from_x && ly.xs[1] == 1 && ly.C % chunk == 0) G = chunk;
       if (tune.group > 0) G = tune.group;
       while (true) {
-        st.smem_bytes = plan_stage(st.plan, ly, Hl[c.first], Wl[c.first], c.first, c.nlev, final_stage, has_rin,
-                                   G, tiled_edge, tiled_edge);
-        if (st.smem_bytes <= kSmemLimitBytes || G == 1) break;
+        st.smem_bytes = plan_stage(st.plan, ly, H, W, c.first, c.nlev, final_stage, has_rin, G, TY, TX, in_shift);
+        if (st.smem_bytes <= kSmemTwoPerSm || G == 1) break;
         G /= 2;
       }
       if (st.smem_bytes > kSmemLimitBytes) { ch.status = -6; return ch; }

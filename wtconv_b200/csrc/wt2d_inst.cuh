@@ -8,7 +8,7 @@
 namespace wt {
 
 template <typename T, int K>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 wt2d_fused_kernel(const __grid_constant__ Plan2d p, const T* __restrict__ x, T* __restrict__ y,
                   const float* __restrict__ packed, const float* __restrict__ rin, float* __restrict__ rout) {
   extern __shared__ __align__(16) float wt_smem[];

@@ -33,6 +33,8 @@ struct Plan2d {
   int has_rin;           // R_d is read from `rin` (fp32 planes) instead of being zero
   int out_planes;        // output is fp32 (B,C,H,W)-contiguous planes (deep launch)
   int out_stride;        // spatial subsampling of the output (final launch only)
+  int in_shift;          // q > 0: the stage's input plane is the 2^q x 2^q block sum of x, formed while loading
+  int Hsrc, Wsrc;        // size of the tensor x actually read (== H, W when in_shift == 0)
   int Hout, Wout;
   // packed parameters
   int wstride;           // floats per channel
@@ -42,12 +44,15 @@ struct Plan2d {
   int TY, TX;            // output tile (multiples of 2^nlev unless a single tile)
   int ntile_y, ntile_x, ngroups;
   int nthreads;
+  int elem_size;         // bytes per element of T (the launch's input / output type)
   // per-level extents, j = 0 (input plane) .. nlev
   int Hj[kMaxFused + 1], Wj[kMaxFused + 1];
   int rows[kMaxFused + 1], pitch[kMaxFused + 1], off[kMaxFused + 1];
   int rrows[kMaxFused + 1], rpitch[kMaxFused + 1], roff[kMaxFused + 1];
   int th[kMaxFused + 1], tw[kMaxFused + 1];   // thread tile per level (j=0: base conv tile)
-  int woff;              // packed weights of the G channels
+  int woff, wsm;         // staged tap sets: offset, floats per channel
+  int yoff, yrows, ypitch;   // Y scratch of the deep levels (4 sub-band arrays per channel)
+  int ooff, orows, opitch;   // OUT staging tile: offset in floats, rows / pitch in elements of T
   int smem_floats;
   // tensor strides in elements (n,c,h,w)
   long long xs[4], ys[4];
