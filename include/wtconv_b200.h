@@ -87,11 +87,17 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype,
                        float* packed, void* stream);
 
 /*
- * Scratch bytes wtconv2d_forward needs for this problem (0 when the whole
- * cascade of a plane is fused on chip, which is the case for every plane up to
- * about 56x56; larger planes keep a coarse low-pass pyramid in scratch).
+ * Scratch bytes wtconv2d_forward needs for this problem and memory layout (0
+ * when the whole cascade of a plane is fused on chip, which is the case for
+ * small planes; larger planes hand the reconstruction of their deep levels --
+ * a quarter-resolution fp32 plane set or smaller -- from one launch to the next
+ * through scratch).  x_strides / y_strides as for wtconv2d_forward (NULL =
+ * NCHW-contiguous); the answer does not depend on pointer alignment.
+ * The reference has no counterpart: its intermediates are torch allocations
+ * inside wtconv/wtconv2d.py:46-78.
  */
-int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, size_t* bytes);
+int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype,
+                             const long long* x_strides, const long long* y_strides, size_t* bytes);
 
 /*
  * WTConv2d forward: y = base_scale*(base_conv(x)) + inverse-wavelet cascade of

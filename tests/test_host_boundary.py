@@ -37,9 +37,11 @@ def test_host_only_entry_points():
     assert lib.wtconv_packed_param_floats(1, 64, 5, 4) == 64 * 8 * 9
     assert "odd" in L.status_string(-2)
     nbytes = ctypes.c_size_t(123)
-    assert lib.wtconv2d_workspace_bytes(128, 96, 56, 56, 5, 5, 1, ctypes.byref(nbytes)) == 0 and nbytes.value == 0
-    assert lib.wtconv2d_workspace_bytes(2, 256, 512, 512, 5, 5, 1, ctypes.byref(nbytes)) == 0 and nbytes.value > 0
-    assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, ctypes.byref(nbytes)) == -2
+    assert lib.wtconv2d_workspace_bytes(128, 192, 28, 28, 5, 4, 1, None, None, ctypes.byref(nbytes)) == 0
+    assert nbytes.value == 0                        # small planes: the whole cascade stays on chip
+    assert lib.wtconv2d_workspace_bytes(2, 256, 512, 512, 5, 5, 1, None, None, ctypes.byref(nbytes)) == 0
+    assert 0 < nbytes.value <= 2 * 256 * 512 * 512 * 4 // 3
+    assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, None, None, ctypes.byref(nbytes)) == -2
 
 
 @pytest.mark.parametrize("name", golden_names())

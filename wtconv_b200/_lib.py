@@ -27,7 +27,7 @@ SYMBOLS = {
     "wtconv_packed_param_floats": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "wtconv_pack_params": (_I, [_I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _VP, _VP, _VP,
                                 ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),
-    "wtconv2d_workspace_bytes": (_I, [_I, _I, _I, _I, _I, _I, _I, ctypes.POINTER(ctypes.c_size_t)]),
+    "wtconv2d_workspace_bytes": (_I, [_I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, ctypes.POINTER(ctypes.c_size_t)]),
     "wtconv2d_forward": (_I, [_VP, _VP, _VP, _VP, ctypes.c_size_t, _I, _I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, _VP]),
     "wtconv1d_forward": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, _VP]),
 }

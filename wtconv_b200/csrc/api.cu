@@ -148,10 +148,13 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double an
   return (int)launch_pack(a, param_dtype, packed, static_cast<cudaStream_t>(stream));
 }
 
-int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, size_t* bytes) {
+int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, const long long* x_strides,
+                             const long long* y_strides, size_t* bytes) {
   if (!bytes) return WTCONV_ERR_BAD_ARG;
   Layer2d ly;
-  const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, nullptr, nullptr);
+  // the stage chain depends on the layout (channel-fastest or not) but not on the output
+  // stride or on pointer alignment
+  const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, x_strides, y_strides);
   if (st) return st;
   const Chain2d ch = plan_layer(ly, env_tuning());
   if (ch.status) return ch.status;

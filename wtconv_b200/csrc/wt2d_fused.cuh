@@ -215,128 +215,285 @@ WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
 }
 
 // ---------------------------------------------------------------------------
-// Channels-last staging: every thread moves CB-byte chunks (CB/sizeof(T)
-// consecutive channels of one pixel) between global memory and planar arrays.
-// Pixels are walked with an incremental (row, col) counter: no division in the loop.
+// Staging of the input tile.  Every cell of the X0 arrays is written: pixels of
+// the plane that the tile needs get their value, everything else (the zero
+// extension of wtconv2d.py:49-51, the 'same' padding, the overhang of partial
+// thread tiles) gets 0 -- so shared memory never has to be cleared.  Work is
+// walked in groups of four consecutive columns with an incremental counter (no
+// division inside the loops) and all global loads of a group are issued before
+// their first use.
 // ---------------------------------------------------------------------------
-template <typename T, int CB>
-WT_HD void load_chunks(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, int nr, int nc,
-                       int pitch, int plane, int tid, int nthr) {
-  constexpr int VEC = Chunk<T, CB>::VEC;
-  if (VEC < 1) return;
-  const int nch = p.G / (VEC > 0 ? VEC : 1);
-  const int total = nr * nc * nch;
-  if (tid >= total) return;
-  // item i = pix * nch + ch
-  int ch = tid % nch, pix = tid / nch;
-  int yy = pix / nc, xx = pix - yy * nc;
-  const int dch = nthr % nch, dpix = nthr / nch;
-  const int dy = dpix / nc, dx = dpix - dy * nc;
-  for (int i = tid; i < total; i += nthr) {
-    Chunk<T, CB> c;
-    c.raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(src + (size_t)yy * p.xs[2] + (size_t)xx * p.xs[3] + ch * VEC);
-    float* dd = dst + (ch * VEC) * plane + yy * pitch + xx;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) dd[e * plane] = Elem<T>::to_f(c.get(e));
-    ch += dch; xx += dx; yy += dy;
-    if (ch >= nch) { ch -= nch; ++xx; }
-    if (xx >= nc) { xx -= nc; ++yy; }
-    if (xx >= nc) { xx -= nc; ++yy; }
-  }
-}
+struct FillRange {   // valid source range in plane coordinates and the array origin
+  int ylo, yhi, xlo, xhi, orgy, orgx;
+};
 
-// Same walk, but every destination cell is the sum of an edge x edge block of source pixels
-// (the low-pass input of a deep stage formed directly from the layer input).
-template <typename T, int CB>
-WT_HD void load_chunks_reduced(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, int y0, int x0,
-                               int nr, int nc, int pitch, int plane, int edge, int tid, int nthr) {
+// Channels-last: one item = four pixels x CB bytes of consecutive channels.
+// EDGE > 1: every pixel is the sum of an EDGE x EDGE block of source pixels (the
+// low-pass input of a deep stage, wtconv2d.py:49-54, formed straight from x).
+template <typename T, int CB, int EDGE>
+WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, const FillRange& fr,
+                          int rows, int pitch, int tid, int nthr) {
   constexpr int VEC = Chunk<T, CB>::VEC;
   if (VEC < 1) return;
-  const int nch = p.G / (VEC > 0 ? VEC : 1);
-  const int total = nr * nc * nch;
+  constexpr int V = VEC > 0 ? VEC : 1;
+  const int nch = p.G / V;
+  const int ngrp = pitch >> 2;
+  const int per_row = ngrp * nch;
+  const int total = rows * per_row;
   if (tid >= total) return;
-  int ch = tid % nch, pix = tid / nch;
-  int yy = pix / nc, xx = pix - yy * nc;
-  const int dch = nthr % nch, dpix = nthr / nch;
-  const int dy = dpix / nc, dx = dpix - dy * nc;
+  const int plane = rows * pitch;
+  int rr = tid / per_row, ci = tid - rr * per_row;
+  const int drr = nthr / per_row, dci = nthr - drr * per_row;
   for (int i = tid; i < total; i += nthr) {
-    float acc[VEC > 0 ? VEC : 1];
+    const int gq = ci / nch, ch = ci - gq * nch;
+    const int py = fr.orgy + rr, px0 = fr.orgx + 4 * gq;
+    const bool rowok = py >= fr.ylo && py < fr.yhi;
+    float v[4][V];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
-    for (int by = 0; by < edge; ++by) {
-      const int sy = (y0 + yy) * edge + by;
-      if (sy >= p.Hsrc) break;
-      float racc[VEC > 0 ? VEC : 1];
+    for (int k = 0; k < 4; ++k)
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) racc[e] = 0.f;
-      for (int bx = 0; bx < edge; ++bx) {
-        const int sx = (x0 + xx) * edge + bx;
-        if (sx >= p.Wsrc) break;
-        Chunk<T, CB> c;
-        c.raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(src + (size_t)sy * p.xs[2] + (size_t)sx * p.xs[3] + ch * VEC);
+      for (int e = 0; e < V; ++e) v[k][e] = 0.f;
+    if (EDGE == 1) {
+      Chunk<T, CB> c[4];
+      bool ok[4];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) racc[e] += Elem<T>::to_f(c.get(e));
+      for (int k = 0; k < 4; ++k) {
+        ok[k] = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
+        if (ok[k])
+          c[k].raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(
+              src + (size_t)py * p.xs[2] + (size_t)(px0 + k) * p.xs[3] + ch * V);
       }
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) acc[e] += racc[e];
-    }
-    float* dd = dst + (ch * VEC) * plane + yy * pitch + xx;
+      for (int k = 0; k < 4; ++k)
+        if (ok[k]) {
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) dd[e * plane] = acc[e];
-    ch += dch; xx += dx; yy += dy;
-    if (ch >= nch) { ch -= nch; ++xx; }
-    if (xx >= nc) { xx -= nc; ++yy; }
-    if (xx >= nc) { xx -= nc; ++yy; }
+          for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
+        }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int px = px0 + k;
+        if (rowok && px >= fr.xlo && px < fr.xhi) {
+          Chunk<T, CB> c[EDGE * EDGE];
+          bool ok[EDGE * EDGE];
+#pragma unroll
+          for (int b = 0; b < EDGE * EDGE; ++b) {
+            const int sy = py * EDGE + b / EDGE, sx = px * EDGE + b % EDGE;
+            ok[b] = sy < p.Hsrc && sx < p.Wsrc;
+            if (ok[b])
+              c[b].raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(
+                  src + (size_t)sy * p.xs[2] + (size_t)sx * p.xs[3] + ch * V);
+          }
+#pragma unroll
+          for (int by = 0; by < EDGE; ++by) {
+            float racc[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) racc[e] = 0.f;
+#pragma unroll
+            for (int bx = 0; bx < EDGE; ++bx)
+              if (ok[by * EDGE + bx]) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) racc[e] += Elem<T>::to_f(c[by * EDGE + bx].get(e));
+              }
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[k][e] += racc[e];
+          }
+        }
+      }
+    }
+    float* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+      *reinterpret_cast<float4*>(dd + e * plane) = make_float4(v[0][e], v[1][e], v[2][e], v[3][e]);
+    rr += drr; ci += dci;
+    if (ci >= per_row) { ci -= per_row; ++rr; }
   }
 }
 
+// Any layout, any reduction edge: one item = four consecutive pixels of one channel.
+// Lanes walk along a row, so NCHW rows are read coalesced (128-bit when aligned).
+template <typename T>
+WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, const FillRange& fr,
+                          int gc, int rows, int pitch, int tid, int nthr) {
+  const int ngrp = pitch >> 2;
+  const int per_g = rows * ngrp;
+  const int total = gc * per_g;
+  if (tid >= total) return;
+  const int edge = 1 << p.in_shift;
+  const bool vec_ok = (edge == 1) && p.xs[3] == 1 && (sizeof(T) == 4) && ((p.xs[2] & 3) == 0) &&
+                      ((p.xs[1] & 3) == 0) && ((p.xs[0] & 3) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  int g = tid / per_g, rem = tid - g * per_g;
+  int rr = rem / ngrp, gq = rem - rr * ngrp;
+  const int dg = nthr / per_g, drem = nthr - dg * per_g;
+  const int drr = drem / ngrp, dgq = drem - drr * ngrp;
+  for (int i = tid; i < total; i += nthr) {
+    const int py = fr.orgy + rr, px0 = fr.orgx + 4 * gq;
+    const bool rowok = py >= fr.ylo && py < fr.yhi;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    const T* sb = src + (size_t)g * p.xs[1];
+    if (rowok) {
+      if (vec_ok && px0 >= fr.xlo && px0 + 3 < fr.xhi && (px0 & 3) == 0) {
+        const float4 t = *reinterpret_cast<const float4*>(sb + (size_t)py * p.xs[2] + px0);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      } else if (edge == 1) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (px0 + k >= fr.xlo && px0 + k < fr.xhi)
+            v[k] = Elem<T>::to_f(sb[(size_t)py * p.xs[2] + (size_t)(px0 + k) * p.xs[3]]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int px = px0 + k;
+          if (px >= fr.xlo && px < fr.xhi) {
+            float acc = 0.f;
+            for (int by = 0; by < edge; ++by) {
+              const int sy = py * edge + by;
+              if (sy >= p.Hsrc) break;
+              float racc = 0.f;
+              for (int bx = 0; bx < edge; ++bx) {
+                const int sx = px * edge + bx;
+                if (sx >= p.Wsrc) break;
+                racc += Elem<T>::to_f(sb[(size_t)sy * p.xs[2] + (size_t)sx * p.xs[3]]);
+              }
+              acc += racc;
+            }
+            v[k] = acc;
+          }
+        }
+      }
+    }
+    *reinterpret_cast<float4*>(dst + g * (rows * pitch) + rr * pitch + 4 * gq) = make_float4(v[0], v[1], v[2], v[3]);
+    g += dg; rr += drr; gq += dgq;
+    if (gq >= ngrp) { gq -= ngrp; ++rr; }
+    if (rr >= rows) { rr -= rows; ++g; }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Haar analysis of one level for the whole array extent (wavelet.py:62-67, raw
+// LL feeds the next level): one item = four consecutive positions of one
+// channel -> four float4 stores (LL, LH, HL, HH).  Positions outside the plane,
+// or whose 2x2 source block is not held on chip, are written as zeros.
+// ---------------------------------------------------------------------------
+template <int K>
+WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j, int gc, int tid,
+                          int nthr) {
+  const int rows = p.rows[j], pitch = p.pitch[j];
+  const int ngrp = pitch >> 2;
+  const int per_g = rows * ngrp;
+  const int total = gc * per_g;
+  if (tid >= total) return;
+  const int sp = p.pitch[j - 1], srows = p.rows[j - 1];
+  const int dplane = rows * pitch;
+  const int Hj = p.Hj[j], Wj = p.Wj[j];
+  int g = tid / per_g, rem = tid - g * per_g;
+  int rr = rem / ngrp, gq = rem - rr * ngrp;
+  const int dg = nthr / per_g, drem = nthr - dg * per_g;
+  const int drr = drem / ngrp, dgq = drem - drr * ngrp;
+  for (int i = tid; i < total; i += nthr) {
+    const int py = ay.org[j] + rr, px0 = ax.org[j] + 4 * gq;
+    const int sy = 2 * py - ay.org[j - 1], sx0 = 2 * px0 - ax.org[j - 1];
+    float o[4][4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[s][k] = 0.f;
+    if (py >= 0 && py < Hj && sy >= 0 && sy + 1 < srows) {
+      const float* s0 = sm.arr(j - 1, g, 0) + sy * sp;
+      float a[8], b[8];
+      const bool full = px0 >= 0 && px0 + 3 < Wj && sx0 >= 0 && sx0 + 7 < sp;
+      if (full && ((K / 2) % 2 == 0)) {          // even radius: source columns are 8-byte aligned
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 t = *reinterpret_cast<const float2*>(s0 + sx0 + 2 * k);
+          const float2 u = *reinterpret_cast<const float2*>(s0 + sp + sx0 + 2 * k);
+          a[2 * k] = t.x; a[2 * k + 1] = t.y; b[2 * k] = u.x; b[2 * k + 1] = u.y;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int px = px0 + k, sx = sx0 + 2 * k;
+          const bool ok = px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
+          a[2 * k] = ok ? s0[sx] : 0.f; a[2 * k + 1] = ok ? s0[sx + 1] : 0.f;
+          b[2 * k] = ok ? s0[sp + sx] : 0.f; b[2 * k + 1] = ok ? s0[sp + sx + 1] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float ab = a[2 * k] + a[2 * k + 1], cd = b[2 * k] + b[2 * k + 1];
+        const float amb = a[2 * k] - a[2 * k + 1], cmd = b[2 * k] - b[2 * k + 1];
+        o[0][k] = ab + cd; o[1][k] = ab - cd; o[2][k] = amb + cmd; o[3][k] = amb - cmd;
+      }
+    }
+    float* od = sm.arr(j, g, 0) + rr * pitch + 4 * gq;
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      *reinterpret_cast<float4*>(od + s * dplane) = make_float4(o[s][0], o[s][1], o[s][2], o[s][3]);
+    g += dg; rr += drr; gq += dgq;
+    if (gq >= ngrp) { gq -= ngrp; ++rr; }
+    if (rr >= rows) { rr -= rows; ++g; }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Channels-last store of the finished tile: one item = two adjacent pixels x CB
+// bytes of consecutive channels, gathered from the planar OUT tile.
+// ---------------------------------------------------------------------------
 template <typename T, int CB>
 WT_HD void store_chunks(const Plan2d& p, T* __restrict__ dst, const T* __restrict__ src, int nr, int nc,
                         int op, int oplane, int s, int tid, int nthr) {
   constexpr int VEC = Chunk<T, CB>::VEC;
   if (VEC < 1) return;
-  const int nch = p.G / (VEC > 0 ? VEC : 1);
-  const int total = nr * nc * nch;
+  constexpr int V = VEC > 0 ? VEC : 1;
+  const int nch = p.G / V;
+  const int npair = (nc + 1) >> 1;
+  const int per_row = npair * nch;
+  const int total = nr * per_row;
   if (tid >= total) return;
-  int ch = tid % nch, pix = tid / nch;
-  int yy = pix / nc, xx = pix - yy * nc;
-  const int dch = nthr % nch, dpix = nthr / nch;
-  const int dy = dpix / nc, dx = dpix - dy * nc;
+  int yy = tid / per_row, ci = tid - yy * per_row;
+  const int dyy = nthr / per_row, dci = nthr - dyy * per_row;
   for (int i = tid; i < total; i += nthr) {
-    const T* ss = src + (ch * VEC) * oplane + (yy * s) * op + xx * s;
-    Chunk<T, CB> c;
+    const int pq = ci / nch, ch = ci - pq * nch;
+    const int xx = 2 * pq;
+    const bool two = xx + 1 < nc;
+    const T* ss = src + (ch * V) * oplane + (yy * s) * op + xx * s;
+    Chunk<T, CB> c0, c1;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) c.set(e, ss[e * oplane]);
-    *reinterpret_cast<typename RawChunk<CB>::type*>(dst + (size_t)yy * p.ys[2] + (size_t)xx * p.ys[3] + ch * VEC) = c.raw;
-    ch += dch; xx += dx; yy += dy;
-    if (ch >= nch) { ch -= nch; ++xx; }
-    if (xx >= nc) { xx -= nc; ++yy; }
-    if (xx >= nc) { xx -= nc; ++yy; }
+    for (int e = 0; e < V; ++e) c0.set(e, ss[e * oplane]);
+    if (two) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) c1.set(e, ss[e * oplane + s]);
+    }
+    T* dd = dst + (size_t)yy * p.ys[2] + (size_t)xx * p.ys[3] + ch * V;
+    *reinterpret_cast<typename RawChunk<CB>::type*>(dd) = c0.raw;
+    if (two) *reinterpret_cast<typename RawChunk<CB>::type*>(dd + p.ys[3]) = c1.raw;
+    yy += dyy; ci += dci;
+    if (ci >= per_row) { ci -= per_row; ++yy; }
   }
 }
 
-// Clears the cells of one level's arrays that lie outside the plane (the zero
-// extension of wtconv2d.py:49-51 and the 'same' padding of the convolutions).
-// One (array, row) pair per step; interior tiles have nothing to clear.
-WT_HD void clear_border(float* __restrict__ arrs, int narr, int rows, int pitch, int orgy, int orgx, int H, int W,
-                        int tid, int nthr) {
-  const bool rows_inside = orgy >= 0 && orgy + rows <= H;
-  const bool cols_inside = orgx >= 0 && orgx + pitch <= W;
-  if (rows_inside && cols_inside) return;
-  const int total = narr * rows;
-  const int left = imin(imax(-orgx, 0), pitch);           // columns [0,left) are outside
-  const int right = imax(imin(W - orgx, pitch), 0);       // columns [right,pitch) are outside
+// Any layout: one item = four consecutive output pixels of one channel.
+template <typename T>
+WT_HD void store_planar(const Plan2d& p, T* __restrict__ dst, const T* __restrict__ src, int gc, int nr, int nc,
+                        int op, int oplane, int s, int tid, int nthr) {
+  const int ngrp = (nc + 3) >> 2;
+  const int per_g = nr * ngrp;
+  const int total = gc * per_g;
+  if (tid >= total) return;
+  int g = tid / per_g, rem = tid - g * per_g;
+  int yy = rem / ngrp, gq = rem - yy * ngrp;
+  const int dg = nthr / per_g, drem = nthr - dg * per_g;
+  const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
   for (int i = tid; i < total; i += nthr) {
-    const int rr = i % rows;
-    float* row = arrs + (size_t)i * pitch;
-    const int py = orgy + rr;
-    if (py < 0 || py >= H) {
-      float4* r4 = reinterpret_cast<float4*>(row);
-      for (int v = 0; v < pitch / 4; ++v) r4[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-    } else {
-      for (int c = 0; c < left; ++c) row[c] = 0.f;
-      for (int c = right; c < pitch; ++c) row[c] = 0.f;
-    }
+    const T* ss = src + g * oplane + (yy * s) * op + (4 * gq) * s;
+    T* dd = dst + (size_t)g * p.ys[1] + (size_t)yy * p.ys[2] + (size_t)(4 * gq) * p.ys[3];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (4 * gq + k < nc) dd[(size_t)k * p.ys[3]] = ss[k * s];
+    g += dg; yy += dyy; gq += dgq;
+    if (gq >= ngrp) { gq -= ngrp; ++yy; }
+    if (yy >= nr) { yy -= nr; ++g; }
   }
 }
 
@@ -368,11 +525,8 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   Smem2d sm{smem, &p};
   T* out_tile = reinterpret_cast<T*>(smem + p.ooff);
 
-  // ---- phase 0: zero borders, stage the tap sets this stage uses, load the input tile
+  // ---- phase 0: stage the tap sets this stage uses, the input tile and the deeper reconstruction
   WT_PHASE(nthr) {
-    for (int j = 0; j <= d; ++j)
-      clear_border(smem + p.off[j], gc * (j == 0 ? 1 : 4), p.rows[j], p.pitch[j], ay.org[j], ax.org[j], p.Hj[j],
-                   p.Wj[j], tid, nthr);
     {
       // per channel: [base set (if any)] [4 sets per level of this stage]
       const int per = p.wsm / 4;                       // float4 per channel in shared memory
@@ -385,115 +539,62 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         reinterpret_cast<float4*>(smem + p.woff)[i] = src[sk];
       }
     }
-    // input tile -> X0 (fp32); cells outside the plane stay zero (wtconv2d.py:49-51)
-    const int y0 = imax(ay.lo[0], 0), y1 = imin(ay.hi[0], p.H);
-    const int x0 = imax(ax.lo[0], 0), x1 = imin(ax.hi[0], p.W);
-    const int nr = y1 - y0, nc = x1 - x0;
-    const int pitch = p.pitch[0];
-    const int plane = p.rows[0] * pitch;
-    float* dst0 = smem + p.off[0] + (y0 - ay.org[0]) * pitch + (x0 - ax.org[0]);
+    // input tile -> X0 (fp32); everything the tile does not take from the plane is zero
+    FillRange fr;
+    fr.ylo = imax(ay.lo[0], 0); fr.yhi = imin(ay.hi[0], p.H);
+    fr.xlo = imax(ax.lo[0], 0); fr.xhi = imin(ax.hi[0], p.W);
+    fr.orgy = ay.org[0]; fr.orgx = ax.org[0];
     const T* xb = x + (size_t)nb * p.xs[0] + (size_t)c0 * p.xs[1];
-    if (p.in_shift > 0) {
-      // low-pass input formed on the fly: un-normalised sum of the 2^q x 2^q source block,
-      // zero outside the source plane (wtconv2d.py:49-54 applied q times, taps folded)
-      const int q = p.in_shift, edge = 1 << q;
-      if (p.x_vec && gc == p.G) {
-        const T* xo = xb;
-        if (p.x_vec == 16) load_chunks_reduced<T, 16>(p, xo, dst0, y0, x0, nr, nc, pitch, plane, edge, tid, nthr);
-        else if (p.x_vec == 8) load_chunks_reduced<T, 8>(p, xo, dst0, y0, x0, nr, nc, pitch, plane, edge, tid, nthr);
-        else load_chunks_reduced<T, 4>(p, xo, dst0, y0, x0, nr, nc, pitch, plane, edge, tid, nthr);
+    float* x0arr = smem + p.off[0];
+    if (p.x_vec && gc == p.G && p.in_shift <= 1) {
+      if (p.in_shift == 0) {
+        if (p.x_vec == 16) fill_x0_chunks<T, 16, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+        else if (p.x_vec == 8) fill_x0_chunks<T, 8, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+        else fill_x0_chunks<T, 4, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
       } else {
-        const int total = nr * nc * gc;
-        const bool cl = p.x_cl != 0;
-        for (int i = tid; i < total; i += nthr) {
-          int g, yy, xx;
-          if (cl) { g = i % gc; const int pix = i / gc; yy = pix / nc; xx = pix - yy * nc; }
-          else { xx = i % nc; const int t = i / nc; yy = t % nr; g = t / nr; }
-          const T* sb = xb + (size_t)g * p.xs[1];
-          float acc = 0.f;
-          for (int dy = 0; dy < edge; ++dy) {
-            const int sy = (y0 + yy) * edge + dy;
-            if (sy >= p.Hsrc) break;
-            float racc = 0.f;
-            for (int dx = 0; dx < edge; ++dx) {
-              const int sx = (x0 + xx) * edge + dx;
-              if (sx >= p.Wsrc) break;
-              racc += Elem<T>::to_f(sb[(size_t)sy * p.xs[2] + (size_t)sx * p.xs[3]]);
-            }
-            acc += racc;
-          }
-          dst0[g * plane + yy * pitch + xx] = acc;
-        }
-      }
-    } else if (p.x_vec && gc == p.G) {
-      const T* xo = xb + (size_t)y0 * p.xs[2] + (size_t)x0 * p.xs[3];
-      if (p.x_vec == 16) load_chunks<T, 16>(p, xo, dst0, nr, nc, pitch, plane, tid, nthr);
-      else if (p.x_vec == 8) load_chunks<T, 8>(p, xo, dst0, nr, nc, pitch, plane, tid, nthr);
-      else load_chunks<T, 4>(p, xo, dst0, nr, nc, pitch, plane, tid, nthr);
-    } else if (p.x_cl) {
-      const int total = nr * nc * gc;
-      for (int i = tid; i < total; i += nthr) {
-        const int g = i % gc;
-        const int pix = i / gc;
-        const int yy = pix / nc, xx = pix - yy * nc;
-        dst0[g * plane + yy * pitch + xx] =
-            Elem<T>::to_f(xb[(size_t)g * p.xs[1] + (size_t)(y0 + yy) * p.xs[2] + (size_t)(x0 + xx) * p.xs[3]]);
+        if (p.x_vec == 16) fill_x0_chunks<T, 16, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+        else if (p.x_vec == 8) fill_x0_chunks<T, 8, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+        else fill_x0_chunks<T, 4, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
       }
     } else {
-      const int total = nr * nc * gc;
-      for (int i = tid; i < total; i += nthr) {
-        const int xx = i % nc;
-        const int t = i / nc;
-        const int yy = t % nr, g = t / nr;
-        dst0[g * plane + yy * pitch + xx] =
-            Elem<T>::to_f(xb[(size_t)g * p.xs[1] + (size_t)(y0 + yy) * p.xs[2] + (size_t)(x0 + xx) * p.xs[3]]);
-      }
+      fill_x0_planar<T>(p, xb, x0arr, fr, gc, p.rows[0], p.pitch[0], tid, nthr);
     }
     // reconstruction of the deeper levels, produced by an earlier launch
     if (p.has_rin) {
       const int hn = ay.n[d], wn = ax.n[d];
-      const int total = gc * hn * wn;
-      const float* rb = rin + ((size_t)nb * p.C + c0) * (size_t)(p.Hj[d] * p.Wj[d]);
-      for (int i = tid; i < total; i += nthr) {
-        const int xx = i % wn;
-        const int t = i / wn;
-        const int yy = t % hn, g = t / hn;
-        sm.rec(d, g)[yy * p.rpitch[d] + xx] =
-            rb[(size_t)g * (p.Hj[d] * p.Wj[d]) + (size_t)(ay.a[d] + yy) * p.Wj[d] + (ax.a[d] + xx)];
+      const int Hd = p.Hj[d], Wd = p.Wj[d];
+      const int ngrp = (wn + 3) >> 2;
+      const int per_g = hn * ngrp;
+      const int total = gc * per_g;
+      const float* rb = rin + ((size_t)nb * p.C + c0) * (size_t)(Hd * Wd) + (size_t)ay.a[d] * Wd + ax.a[d];
+      const bool vec_ok = ((Wd & 3) == 0) && ((ax.a[d] & 3) == 0) && ((Hd * Wd) % 4 == 0);
+      if (tid < total) {
+        int g = tid / per_g, rem = tid - g * per_g;
+        int yy = rem / ngrp, gq = rem - yy * ngrp;
+        const int dg = nthr / per_g, drem = nthr - dg * per_g;
+        const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
+        for (int i = tid; i < total; i += nthr) {
+          const float* rs = rb + (size_t)g * (Hd * Wd) + (size_t)yy * Wd + 4 * gq;
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (vec_ok && 4 * gq + 3 < wn) t = *reinterpret_cast<const float4*>(rs);
+          else {
+            if (4 * gq + 0 < wn) t.x = rs[0];
+            if (4 * gq + 1 < wn) t.y = rs[1];
+            if (4 * gq + 2 < wn) t.z = rs[2];
+            if (4 * gq + 3 < wn) t.w = rs[3];
+          }
+          *reinterpret_cast<float4*>(sm.rec(d, g) + yy * p.rpitch[d] + 4 * gq) = t;
+          g += dg; yy += dyy; gq += dgq;
+          if (gq >= ngrp) { gq -= ngrp; ++yy; }
+          if (yy >= hn) { yy -= hn; ++g; }
+        }
       }
     }
   }
 
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
-    WT_PHASE(nthr) {
-      const int y0 = imax(ay.lo[j], 0), y1 = imin(ay.hi[j], p.Hj[j]);
-      const int x0 = imax(ax.lo[j], 0), x1 = imin(ax.hi[j], p.Wj[j]);
-      const int nr = y1 - y0, nc = x1 - x0;
-      const int total = gc * nr * nc;
-      const int sp = p.pitch[j - 1], dp = p.pitch[j];
-      const int dplane = p.rows[j] * dp;
-      if (tid < total) {
-        int xx = tid % nc, t = tid / nc;
-        int yy = t % nr, g = t / nr;
-        const int dx = nthr % nc, dt = nthr / nc;
-        const int dy = dt % nr, dg = dt / nr;
-        for (int i = tid; i < total; i += nthr) {
-          const float* s = sm.arr(j - 1, g, 0) + (2 * (y0 + yy) - ay.org[j - 1]) * sp + (2 * (x0 + xx) - ax.org[j - 1]);
-          const float a = s[0], b = s[1], c = s[sp], e = s[sp + 1];
-          float* o = sm.arr(j, g, 0) + (y0 + yy - ay.org[j]) * dp + (x0 + xx - ax.org[j]);
-          const float ab = a + b, cd = c + e, amb = a - b, cmd = c - e;
-          o[0] = ab + cd;            // LL
-          o[dplane] = ab - cd;       // LH
-          o[2 * dplane] = amb + cmd; // HL
-          o[3 * dplane] = amb - cmd; // HH
-          xx += dx; yy += dy; g += dg;
-          if (xx >= nc) { xx -= nc; ++yy; }
-          if (yy >= nr) { yy -= nr; ++g; }
-          if (yy >= nr) { yy -= nr; ++g; }
-        }
-      }
-    }
+    WT_PHASE(nthr) { analysis_level<K>(p, sm, ay, ax, j, gc, tid, nthr); }
   }
 
   // ---- phase 2: deep levels bottom-up: per-sub-band convolutions into Y, then the
@@ -575,13 +676,30 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       const int rplane = p.rrows[0] * rp;
       const float* r0 = smem + p.roff[0];
       const int hn = ay.n[0], wn = ax.n[0];
-      const int total = gc * hn * wn;
-      float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W);
-      for (int i = tid; i < total; i += nthr) {
-        const int xx = i % wn;
-        const int t = i / wn;
-        const int yy = t % hn, g = t / hn;
-        ob[(size_t)g * (p.H * p.W) + (size_t)(ay.t0 + yy) * p.W + (ax.t0 + xx)] = r0[g * rplane + yy * rp + xx];
+      const int ngrp = (wn + 3) >> 2;
+      const int per_g = hn * ngrp;
+      const int total = gc * per_g;
+      float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)ay.t0 * p.W + ax.t0;
+      const bool vec_ok = ((p.W & 3) == 0) && ((ax.t0 & 3) == 0) && ((p.H * p.W) % 4 == 0);
+      if (tid < total) {
+        int g = tid / per_g, rem = tid - g * per_g;
+        int yy = rem / ngrp, gq = rem - yy * ngrp;
+        const int dg = nthr / per_g, drem = nthr - dg * per_g;
+        const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
+        for (int i = tid; i < total; i += nthr) {
+          const float4 t = *reinterpret_cast<const float4*>(r0 + g * rplane + yy * rp + 4 * gq);
+          float* od = ob + (size_t)g * (p.H * p.W) + (size_t)yy * p.W + 4 * gq;
+          if (vec_ok && 4 * gq + 3 < wn) *reinterpret_cast<float4*>(od) = t;
+          else {
+            if (4 * gq + 0 < wn) od[0] = t.x;
+            if (4 * gq + 1 < wn) od[1] = t.y;
+            if (4 * gq + 2 < wn) od[2] = t.z;
+            if (4 * gq + 3 < wn) od[3] = t.w;
+          }
+          g += dg; yy += dyy; gq += dgq;
+          if (gq >= ngrp) { gq -= ngrp; ++yy; }
+          if (yy >= hn) { yy -= hn; ++g; }
+        }
       }
     } else {
       const int op = p.opitch;
@@ -590,31 +708,14 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       const int oy0 = cdiv(ay.t0, s), oy1 = cdiv(ay.t1, s);
       const int ox0 = cdiv(ax.t0, s), ox1 = cdiv(ax.t1, s);
       const int nr = oy1 - oy0, nc = ox1 - ox0;
-      T* yb = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1];
+      T* yb = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1] + (size_t)oy0 * p.ys[2] + (size_t)ox0 * p.ys[3];
       const T* o0 = out_tile + (oy0 * s - ay.t0) * op + (ox0 * s - ax.t0);
       if (p.y_vec && gc == p.G) {
-        T* yo = yb + (size_t)oy0 * p.ys[2] + (size_t)ox0 * p.ys[3];
-        if (p.y_vec == 16) store_chunks<T, 16>(p, yo, o0, nr, nc, op, oplane, s, tid, nthr);
-        else if (p.y_vec == 8) store_chunks<T, 8>(p, yo, o0, nr, nc, op, oplane, s, tid, nthr);
-        else store_chunks<T, 4>(p, yo, o0, nr, nc, op, oplane, s, tid, nthr);
-      } else if (p.y_cl) {
-        const int total = nr * nc * gc;
-        for (int i = tid; i < total; i += nthr) {
-          const int g = i % gc;
-          const int pix = i / gc;
-          const int yy = pix / nc, xx = pix - yy * nc;
-          yb[(size_t)g * p.ys[1] + (size_t)(oy0 + yy) * p.ys[2] + (size_t)(ox0 + xx) * p.ys[3]] =
-              o0[g * oplane + (yy * s) * op + xx * s];
-        }
+        if (p.y_vec == 16) store_chunks<T, 16>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
+        else if (p.y_vec == 8) store_chunks<T, 8>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
+        else store_chunks<T, 4>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
       } else {
-        const int total = nr * nc * gc;
-        for (int i = tid; i < total; i += nthr) {
-          const int xx = i % nc;
-          const int t = i / nc;
-          const int yy = t % nr, g = t / nr;
-          yb[(size_t)g * p.ys[1] + (size_t)(oy0 + yy) * p.ys[2] + (size_t)(ox0 + xx) * p.ys[3]] =
-              o0[g * oplane + (yy * s) * op + xx * s];
-        }
+        store_planar<T>(p, yb, o0, gc, nr, nc, op, oplane, s, tid, nthr);
       }
     }
   }

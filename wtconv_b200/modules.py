@@ -180,16 +180,16 @@ class WTConv2d(_WTConvNd):
                         memory_format=torch.channels_last if channels_last else torch.contiguous_format)
         packed = self._packed_params(x.device)
         K, L, code = self.kernel_size, self.wt_levels, _DTYPE_CODE[x.dtype]
-        key = (B, C, H, W, code)
+        xs = (ctypes.c_longlong * 4)(*x.stride())
+        ys = (ctypes.c_longlong * 4)(*y.stride())
+        key = (B, C, H, W, code, channels_last)
         nbytes = self._ws_cache.get(key)
         if nbytes is None:
             out = ctypes.c_size_t(0)
-            _lib.check(lib.wtconv2d_workspace_bytes(B, C, H, W, K, L, code, ctypes.byref(out)),
+            _lib.check(lib.wtconv2d_workspace_bytes(B, C, H, W, K, L, code, xs, ys, ctypes.byref(out)),
                        "wtconv2d_workspace_bytes")
             nbytes = self._ws_cache[key] = int(out.value)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
-        xs = (ctypes.c_longlong * 4)(*x.stride())
-        ys = (ctypes.c_longlong * 4)(*y.stride())
         with torch.cuda.device(x.device):
             stream = torch.cuda.current_stream(x.device).cuda_stream
             st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
