@@ -33,7 +33,8 @@ void run2d(const Plan2d& p, const void* x, void* y, const float* packed, const f
   for (long long b = 0; b < blocks; ++b) {
     // poison the buffer so that a cell the kernel forgets to clear shows up
     for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
-    wt2d_cta<T, K>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
+    if (p.has_base) wt2d_cta<T, K, true>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
+    else wt2d_cta<T, K, false>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
   }
 }
 

@@ -6,10 +6,13 @@
 // bottom-up inverse transform with the low-pass accumulation, the base
 // depthwise convolution with its scale and bias, the final add and the stride.
 //
-// Shared-memory data layout (planar per channel g):
-//   X0[g]            fp32  input tile with zero border (level 0)
-//   S_j[g][s]        fp32  un-normalised Haar sub-bands of level j, s = LL,LH,HL,HH
-//   Y[g][s]          fp32  scaled sub-band convolutions of one deep level (scratch)
+// Shared-memory data layout (planar per channel g, planes padded so that the
+// eight lanes of a quarter warp, which work on eight different channels, hit
+// eight different 16-byte bank groups):
+//   X0[g]            input tile with zero border; kept in the activation type when it
+//                    is 16-bit and comes straight from x, fp32 otherwise
+//   S_j[s][g]        fp32  un-normalised Haar sub-bands of level j, s = LL,LH,HL,HH
+//   Y[s][g]          fp32  scaled sub-band convolutions of one deep level (scratch)
 //   R_j[g]           fp32  reconstruction accumulated at level j
 //   OUT[g]           T     finished output tile, staged for coalesced stores
 // The Haar taps are not applied here: the packed parameters carry the product
@@ -22,23 +25,62 @@
 //     four sub-band convolutions, the synthesis butterfly and the 4x8-pixel base
 //     convolution all stay in registers, 64 accumulators per thread;
 //   * deeper levels are small: one item is one sub-band of a 2x4 / 4x4 tile, the
-//     four sub-bands meet again in shared memory for the synthesis butterfly.
+//     four sub-bands meet again in shared memory for the synthesis butterfly;
+//   * staging phases (load, analysis, store) move four pixels per step with
+//     128-bit accesses and write every cell of their arrays, so nothing is cleared.
 #pragma once
 
 #include "wt2d_plan.h"
 
 namespace wt {
 
+template <bool B, typename A, typename C> struct Select { typedef A type; };
+template <typename A, typename C> struct Select<false, A, C> { typedef C type; };
+
+// four consecutive elements of a shared-memory row
+WT_HD void load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <typename H>
+WT_HD void load4(const H* p, float (&v)[4]) {
+  Chunk<H, 8> c;
+  c.raw = *reinterpret_cast<const uint2*>(p);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) v[e] = Elem<H>::to_f(c.get(e));
+}
+WT_HD void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <typename H>
+WT_HD void store4(H* p, float a, float b, float c, float d) {
+  Chunk<H, 8> k;
+  k.set(0, Elem<H>::from_f(a)); k.set(1, Elem<H>::from_f(b));
+  k.set(2, Elem<H>::from_f(c)); k.set(3, Elem<H>::from_f(d));
+  *reinterpret_cast<uint2*>(p) = k.raw;
+}
+// two consecutive elements (8-byte / 4-byte aligned)
+WT_HD void load2(const float* p, float& a, float& b) {
+  const float2 t = *reinterpret_cast<const float2*>(p);
+  a = t.x; b = t.y;
+}
+template <typename H>
+WT_HD void load2(const H* p, float& a, float& b) {
+  Chunk<H, 4> c;
+  c.raw = *reinterpret_cast<const unsigned int*>(p);
+  a = Elem<H>::to_f(c.get(0)); b = Elem<H>::to_f(c.get(1));
+}
+
 // ---------------------------------------------------------------------------
 // Register-tiled depthwise KxK cross-correlation of a TH x TW tile.
-// `src` points at the top-left element of the (TH+K-1) x (TW+K-1) window, 16-byte
-// aligned; rows are `pitch` floats apart (pitch % 4 == 0).  The window is read
-// with 128-bit shared-memory loads, one input row at a time, and every row is
-// applied to all output rows it contributes to, so each loaded float feeds
+// `src` points at the top-left element of the (TH+K-1) x (TW+K-1) window, aligned
+// to four elements; rows are `pitch` elements apart (pitch % 4 == 0).  One input
+// row at a time is read with 128-bit (fp32) / 64-bit (16-bit source) loads and
+// applied to all output rows it contributes to, so each loaded element feeds
 // about K*min(K,TH)*TW/(TW+K-1) FMAs.
 // ---------------------------------------------------------------------------
-template <int K, int TH, int TW>
-WT_HD void conv_tile(const float* __restrict__ src, int pitch, const float* __restrict__ wts,
+template <int K, int TH, int TW, typename ST>
+WT_HD void conv_tile(const ST* __restrict__ src, int pitch, const float* __restrict__ wts,
                      float (&acc)[TH][TW]) {
   constexpr int WIN = TW + K - 1;
   constexpr int NV = (WIN + 3) / 4;
@@ -52,11 +94,11 @@ WT_HD void conv_tile(const float* __restrict__ src, int pitch, const float* __re
 #pragma unroll
   for (int rr = 0; rr < TH + K - 1; ++rr) {
     float row[NV * 4];
-    const float4* p4 = reinterpret_cast<const float4*>(src + rr * pitch);
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-      const float4 t = p4[v];
-      row[4 * v + 0] = t.x; row[4 * v + 1] = t.y; row[4 * v + 2] = t.z; row[4 * v + 3] = t.w;
+      float t[4];
+      load4(src + rr * pitch + 4 * v, t);
+      row[4 * v + 0] = t[0]; row[4 * v + 1] = t[1]; row[4 * v + 2] = t[2]; row[4 * v + 3] = t[3];
     }
 #pragma unroll
     for (int i = 0; i < K; ++i) {
@@ -75,17 +117,13 @@ WT_HD void conv_tile(const float* __restrict__ src, int pitch, const float* __re
 struct Smem2d {
   float* base;
   const Plan2d* p;
-  // sub-band array s of channel g at level j (j = 0 has a single array, s = 0)
-  WT_HD float* arr(int j, int g, int s) const {
-    const int ns = (j == 0) ? 1 : 4;
-    return base + p->off[j] + (g * ns + s) * (p->rows[j] * p->pitch[j]);
-  }
-  WT_HD float* rec(int j, int g) const { return base + p->roff[j] + g * (p->rrows[j] * p->rpitch[j]); }
-  WT_HD float* ybuf(int g, int s) const { return base + p->yoff + (g * 4 + s) * (p->yrows * p->ypitch); }
-  WT_HD float* weights(int g) const { return base + p->woff + g * p->wsm; }
+  template <typename XT> WT_HD XT* x0(int g) const { return reinterpret_cast<XT*>(base + p->off[0]) + g * p->plane[0]; }
+  WT_HD float* sub(int j, int g, int s) const { return base + p->off[j] + (s * p->G + g) * p->plane[j]; }
+  WT_HD float* rec(int j, int g) const { return base + p->roff[j] + g * p->rplane[j]; }
+  WT_HD float* ybuf(int g, int s) const { return base + p->yoff + (s * p->G + g) * p->yplane; }
   // tap set of level j (1-based within the stage), sub-band s; j = 0: base set
   WT_HD const float* taps(int g, int j, int s) const {
-    return weights(g) + p->tapset * (j == 0 ? 0 : p->has_base + 4 * (j - 1) + s);
+    return base + p->woff + g * p->wsm + p->tapset * (j == 0 ? 0 : p->has_base + 4 * (j - 1) + s);
   }
 };
 
@@ -96,16 +134,17 @@ WT_HD void synth4(float ll, float lh, float hl, float hh, float& o00, float& o01
 }
 
 // ---------------------------------------------------------------------------
-// Top-level item: TH x TW positions of level 1 of this stage for one channel.
+// Top-level item: 2 x 4 positions of level 1 of this stage for one channel.
 // Four scaled sub-band convolutions, low-pass accumulation of the deeper
-// reconstruction (wtconv2d.py:71) and the synthesis butterfly give the
-// 2TH x 2TW block of R_0 in registers.  With FUSE_BASE the base convolution and
-// bias (wtconv2d.py:81-82) are accumulated on top and the finished block goes to
-// the OUT staging tile; otherwise the block is written to R_0 (cropped).
+// reconstruction (wtconv2d.py:71) and the synthesis butterfly give the 4 x 8
+// block of R_0 in registers.  With FUSE_BASE the base convolution and bias
+// (wtconv2d.py:81-82) are accumulated on top and the finished block goes to the
+// OUT staging tile; otherwise the block is written to R_0 (cropped).
 // ---------------------------------------------------------------------------
-template <typename T, int K, int TH, int TW, bool FUSE_BASE>
+template <typename T, typename XT, int K, bool FUSE_BASE>
 WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int g, int iy, int ix,
                     bool has_r, T* __restrict__ out_tile) {
+  constexpr int TH = 2, TW = 4;
   const int r = p.r;
   float acc[2 * TH][2 * TW];
   {
@@ -119,15 +158,15 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
       for (int i = 0; i < TH; ++i)
 #pragma unroll
         for (int q = 0; q < TW; ++q) y[s][i][q] = 0.f;
-      conv_tile<K, TH, TW>(sm.arr(1, g, s) + wy * pitch + wx, pitch, sm.taps(g, 1, s), y[s]);
+      conv_tile<K, TH, TW, float>(sm.sub(1, g, s) + wy * pitch + wx, pitch, sm.taps(g, 1, s), y[s]);
     }
     if (has_r) {
       const float* rj = sm.rec(1, g) + (iy * TH) * p.rpitch[1] + ix * TW;
 #pragma unroll
       for (int i = 0; i < TH; ++i) {
-        const float4 t = *reinterpret_cast<const float4*>(rj + i * p.rpitch[1]);
-        static_assert(TW == 4, "top items are four positions wide");
-        y[0][i][0] += t.x; y[0][i][1] += t.y; y[0][i][2] += t.z; y[0][i][3] += t.w;
+        float t[4];
+        load4(rj + i * p.rpitch[1], t);
+        y[0][i][0] += t[0]; y[0][i][1] += t[1]; y[0][i][2] += t[2]; y[0][i][3] += t[3];
       }
     }
 #pragma unroll
@@ -147,14 +186,14 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
     for (int i = 0; i < 2 * TH; ++i)
 #pragma unroll
       for (int q = 0; q < 2 * TW; ++q) acc[i][q] += bias;
-    conv_tile<K, 2 * TH, 2 * TW>(sm.arr(0, g, 0) + wy * pitch + wx, pitch, wts, acc);
-    // finished pixels -> OUT[g] (type T); the tile is allocated with the overhang of
-    // partial items, so no predicate is needed
-    T* o = out_tile + (size_t)g * (p.orows * p.opitch) + (iy * 2 * TH) * p.opitch + ix * 2 * TW;
+    conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy * pitch + wx, pitch, wts, acc);
+    // finished pixels -> OUT[g]; the tile is allocated with the overhang of partial items
+    T* o = out_tile + g * p.oplane + (iy * 2 * TH) * p.opitch + ix * 2 * TW;
 #pragma unroll
-    for (int i = 0; i < 2 * TH; ++i)
-#pragma unroll
-      for (int q = 0; q < 2 * TW; ++q) o[i * p.opitch + q] = Elem<T>::from_f(acc[i][q]);
+    for (int i = 0; i < 2 * TH; ++i) {
+      store4(o + i * p.opitch, acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      store4(o + i * p.opitch + 4, acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
   } else {
     float* out = sm.rec(0, g);
     const int opitch = p.rpitch[0];
@@ -171,10 +210,11 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
   }
 }
 
-// Base-only layer (wt_levels == 0 in this stage): OUT = bias + base conv.
-template <typename T, int K, int BH, int BW>
+// Base-only layer (no wavelet level in this stage): OUT = bias + base conv.
+template <typename T, typename XT, int K>
 WT_HD void base_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int g, int iy, int ix,
                      T* __restrict__ out_tile) {
+  constexpr int BH = 4, BW = 8;
   const int r = p.r;
   const int pitch = p.pitch[0];
   const int wy = ay.t0 + iy * BH - r - ay.org[0];
@@ -186,15 +226,16 @@ WT_HD void base_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
   for (int i = 0; i < BH; ++i)
 #pragma unroll
     for (int q = 0; q < BW; ++q) acc[i][q] = bias;
-  conv_tile<K, BH, BW>(sm.arr(0, g, 0) + wy * pitch + wx, pitch, wts, acc);
-  T* o = out_tile + (size_t)g * (p.orows * p.opitch) + (iy * BH) * p.opitch + ix * BW;
+  conv_tile<K, BH, BW, XT>(sm.x0<XT>(g) + wy * pitch + wx, pitch, wts, acc);
+  T* o = out_tile + g * p.oplane + (iy * BH) * p.opitch + ix * BW;
 #pragma unroll
-  for (int i = 0; i < BH; ++i)
-#pragma unroll
-    for (int q = 0; q < BW; ++q) o[i * p.opitch + q] = Elem<T>::from_f(acc[i][q]);
+  for (int i = 0; i < BH; ++i) {
+    store4(o + i * p.opitch, acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    store4(o + i * p.opitch + 4, acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+  }
 }
 
-// Deep-level item: one sub-band s of a TH x 4 tile of level j -> Y[g][s]
+// Deep-level item: one sub-band s of a TH x 4 tile of level j -> Y[s][g]
 template <int K, int TH>
 WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j, int g, int s,
                      int iy, int ix) {
@@ -207,11 +248,10 @@ WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
   for (int i = 0; i < TH; ++i)
 #pragma unroll
     for (int q = 0; q < 4; ++q) y[i][q] = 0.f;
-  conv_tile<K, TH, 4>(sm.arr(j, g, s) + wy * pitch + wx, pitch, sm.taps(g, j, s), y);
+  conv_tile<K, TH, 4, float>(sm.sub(j, g, s) + wy * pitch + wx, pitch, sm.taps(g, j, s), y);
   float* o = sm.ybuf(g, s) + (iy * TH) * p.ypitch + ix * 4;
 #pragma unroll
-  for (int i = 0; i < TH; ++i)
-    *reinterpret_cast<float4*>(o + i * p.ypitch) = make_float4(y[i][0], y[i][1], y[i][2], y[i][3]);
+  for (int i = 0; i < TH; ++i) store4(o + i * p.ypitch, y[i][0], y[i][1], y[i][2], y[i][3]);
 }
 
 // ---------------------------------------------------------------------------
@@ -230,59 +270,71 @@ struct FillRange {   // valid source range in plane coordinates and the array or
 // Channels-last: one item = four pixels x CB bytes of consecutive channels.
 // EDGE > 1: every pixel is the sum of an EDGE x EDGE block of source pixels (the
 // low-pass input of a deep stage, wtconv2d.py:49-54, formed straight from x).
-template <typename T, int CB, int EDGE>
-WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, const FillRange& fr,
-                          int rows, int pitch, int tid, int nthr) {
+template <typename T, typename XT, int CB, int EDGE>
+WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, XT* __restrict__ dst, const FillRange& fr,
+                          int tid, int nthr) {
   constexpr int VEC = Chunk<T, CB>::VEC;
   if (VEC < 1) return;
   constexpr int V = VEC > 0 ? VEC : 1;
+  typedef typename RawChunk<CB>::type Raw;
+  const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
   const int nch = p.G / V;
   const int ngrp = pitch >> 2;
   const int per_row = ngrp * nch;
   const int total = rows * per_row;
   if (tid >= total) return;
-  const int plane = rows * pitch;
+  const int xs2 = (int)p.xs[2], xs3 = (int)p.xs[3];
   int rr = tid / per_row, ci = tid - rr * per_row;
   const int drr = nthr / per_row, dci = nthr - drr * per_row;
   for (int i = tid; i < total; i += nthr) {
-    const int gq = ci / nch, ch = ci - gq * nch;
+    const int gq = (nch == 1) ? ci : ci / nch;
+    const int ch = (nch == 1) ? 0 : ci - gq * nch;
     const int py = fr.orgy + rr, px0 = fr.orgx + 4 * gq;
     const bool rowok = py >= fr.ylo && py < fr.yhi;
+    XT* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
     float v[4][V];
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-      for (int e = 0; e < V; ++e) v[k][e] = 0.f;
     if (EDGE == 1) {
       Chunk<T, CB> c[4];
-      bool ok[4];
+      const T* s0 = src + py * xs2 + px0 * xs3 + ch * V;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        ok[k] = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
-        if (ok[k])
-          c[k].raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(
-              src + (size_t)py * p.xs[2] + (size_t)(px0 + k) * p.xs[3] + ch * V);
+        const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
+        if (ok) c[k].raw = *reinterpret_cast<const Raw*>(s0 + k * xs3);
+        else {
+#pragma unroll
+          for (int e = 0; e < V; ++e) c[k].set(e, Elem<T>::from_f(0.f));
+        }
+      }
+      if constexpr (sizeof(XT) == 2) {
+        // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          Chunk<T, 8> q;
+          q.set(0, c[0].get(e)); q.set(1, c[1].get(e)); q.set(2, c[2].get(e)); q.set(3, c[3].get(e));
+          *reinterpret_cast<uint2*>(dd + e * plane) = q.raw;
+        }
+        rr += drr; ci += dci;
+        if (ci >= per_row) { ci -= per_row; ++rr; }
+        continue;
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (ok[k]) {
 #pragma unroll
-          for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
-        }
+        for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
     } else {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[k][e] = 0.f;
         const int px = px0 + k;
         if (rowok && px >= fr.xlo && px < fr.xhi) {
           Chunk<T, CB> c[EDGE * EDGE];
           bool ok[EDGE * EDGE];
+          const T* s0 = src + (py * EDGE) * xs2 + (px * EDGE) * xs3 + ch * V;
 #pragma unroll
           for (int b = 0; b < EDGE * EDGE; ++b) {
-            const int sy = py * EDGE + b / EDGE, sx = px * EDGE + b % EDGE;
-            ok[b] = sy < p.Hsrc && sx < p.Wsrc;
-            if (ok[b])
-              c[b].raw = *reinterpret_cast<const typename RawChunk<CB>::type*>(
-                  src + (size_t)sy * p.xs[2] + (size_t)sx * p.xs[3] + ch * V);
+            ok[b] = (py * EDGE + b / EDGE) < p.Hsrc && (px * EDGE + b % EDGE) < p.Wsrc;
+            if (ok[b]) c[b].raw = *reinterpret_cast<const Raw*>(s0 + (b / EDGE) * xs2 + (b % EDGE) * xs3);
           }
 #pragma unroll
           for (int by = 0; by < EDGE; ++by) {
@@ -301,10 +353,8 @@ WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, float* __r
         }
       }
     }
-    float* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
 #pragma unroll
-    for (int e = 0; e < V; ++e)
-      *reinterpret_cast<float4*>(dd + e * plane) = make_float4(v[0][e], v[1][e], v[2][e], v[3][e]);
+    for (int e = 0; e < V; ++e) store4(dd + e * plane, v[0][e], v[1][e], v[2][e], v[3][e]);
     rr += drr; ci += dci;
     if (ci >= per_row) { ci -= per_row; ++rr; }
   }
@@ -312,9 +362,10 @@ WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, float* __r
 
 // Any layout, any reduction edge: one item = four consecutive pixels of one channel.
 // Lanes walk along a row, so NCHW rows are read coalesced (128-bit when aligned).
-template <typename T>
-WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst, const FillRange& fr,
-                          int gc, int rows, int pitch, int tid, int nthr) {
+template <typename T, typename XT>
+WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, XT* __restrict__ dst, const FillRange& fr,
+                          int gc, int tid, int nthr) {
+  const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
   const int ngrp = pitch >> 2;
   const int per_g = rows * ngrp;
   const int total = gc * per_g;
@@ -363,7 +414,7 @@ WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, float* __r
         }
       }
     }
-    *reinterpret_cast<float4*>(dst + g * (rows * pitch) + rr * pitch + 4 * gq) = make_float4(v[0], v[1], v[2], v[3]);
+    store4(dst + g * plane + rr * pitch + 4 * gq, v[0], v[1], v[2], v[3]);
     g += dg; rr += drr; gq += dgq;
     if (gq >= ngrp) { gq -= ngrp; ++rr; }
     if (rr >= rows) { rr -= rows; ++g; }
@@ -373,19 +424,20 @@ WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, float* __r
 // ---------------------------------------------------------------------------
 // Haar analysis of one level for the whole array extent (wavelet.py:62-67, raw
 // LL feeds the next level): one item = four consecutive positions of one
-// channel -> four float4 stores (LL, LH, HL, HH).  Positions outside the plane,
+// channel -> four 128-bit stores (LL, LH, HL, HH).  Positions outside the plane,
 // or whose 2x2 source block is not held on chip, are written as zeros.
+// `src0` is the first source plane (channel 0), `splane` the channel stride.
 // ---------------------------------------------------------------------------
-template <int K>
-WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j, int gc, int tid,
-                          int nthr) {
+template <int K, typename ST>
+WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j,
+                          const ST* __restrict__ src0, int splane, int gc, int tid, int nthr) {
   const int rows = p.rows[j], pitch = p.pitch[j];
   const int ngrp = pitch >> 2;
   const int per_g = rows * ngrp;
   const int total = gc * per_g;
   if (tid >= total) return;
   const int sp = p.pitch[j - 1], srows = p.rows[j - 1];
-  const int dplane = rows * pitch;
+  const int dstep = p.G * p.plane[j];                    // distance between sub-band groups
   const int Hj = p.Hj[j], Wj = p.Wj[j];
   int g = tid / per_g, rem = tid - g * per_g;
   int rr = rem / ngrp, gq = rem - rr * ngrp;
@@ -400,23 +452,24 @@ WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, con
 #pragma unroll
       for (int k = 0; k < 4; ++k) o[s][k] = 0.f;
     if (py >= 0 && py < Hj && sy >= 0 && sy + 1 < srows) {
-      const float* s0 = sm.arr(j - 1, g, 0) + sy * sp;
+      const ST* s0 = src0 + g * splane + sy * sp;
       float a[8], b[8];
       const bool full = px0 >= 0 && px0 + 3 < Wj && sx0 >= 0 && sx0 + 7 < sp;
-      if (full && ((K / 2) % 2 == 0)) {          // even radius: source columns are 8-byte aligned
+      if (full && ((K / 2) % 2 == 0)) {          // even radius: source column pairs are aligned
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 t = *reinterpret_cast<const float2*>(s0 + sx0 + 2 * k);
-          const float2 u = *reinterpret_cast<const float2*>(s0 + sp + sx0 + 2 * k);
-          a[2 * k] = t.x; a[2 * k + 1] = t.y; b[2 * k] = u.x; b[2 * k + 1] = u.y;
+          load2(s0 + sx0 + 2 * k, a[2 * k], a[2 * k + 1]);
+          load2(s0 + sp + sx0 + 2 * k, b[2 * k], b[2 * k + 1]);
         }
       } else {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int px = px0 + k, sx = sx0 + 2 * k;
           const bool ok = px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
-          a[2 * k] = ok ? s0[sx] : 0.f; a[2 * k + 1] = ok ? s0[sx + 1] : 0.f;
-          b[2 * k] = ok ? s0[sp + sx] : 0.f; b[2 * k + 1] = ok ? s0[sp + sx + 1] : 0.f;
+          a[2 * k] = ok ? Elem<ST>::to_f(s0[sx]) : 0.f;
+          a[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sx + 1]) : 0.f;
+          b[2 * k] = ok ? Elem<ST>::to_f(s0[sp + sx]) : 0.f;
+          b[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sp + sx + 1]) : 0.f;
         }
       }
 #pragma unroll
@@ -426,10 +479,9 @@ WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, con
         o[0][k] = ab + cd; o[1][k] = ab - cd; o[2][k] = amb + cmd; o[3][k] = amb - cmd;
       }
     }
-    float* od = sm.arr(j, g, 0) + rr * pitch + 4 * gq;
+    float* od = sm.sub(j, g, 0) + rr * pitch + 4 * gq;
 #pragma unroll
-    for (int s = 0; s < 4; ++s)
-      *reinterpret_cast<float4*>(od + s * dplane) = make_float4(o[s][0], o[s][1], o[s][2], o[s][3]);
+    for (int s = 0; s < 4; ++s) store4(od + s * dstep, o[s][0], o[s][1], o[s][2], o[s][3]);
     g += dg; rr += drr; gq += dgq;
     if (gq >= ngrp) { gq -= ngrp; ++rr; }
     if (rr >= rows) { rr -= rows; ++g; }
@@ -442,32 +494,45 @@ WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, con
 // ---------------------------------------------------------------------------
 template <typename T, int CB>
 WT_HD void store_chunks(const Plan2d& p, T* __restrict__ dst, const T* __restrict__ src, int nr, int nc,
-                        int op, int oplane, int s, int tid, int nthr) {
+                        int s, int tid, int nthr) {
   constexpr int VEC = Chunk<T, CB>::VEC;
   if (VEC < 1) return;
   constexpr int V = VEC > 0 ? VEC : 1;
+  typedef typename RawChunk<CB>::type Raw;
+  const int op = p.opitch, oplane = p.oplane;
   const int nch = p.G / V;
   const int npair = (nc + 1) >> 1;
   const int per_row = npair * nch;
   const int total = nr * per_row;
   if (tid >= total) return;
+  const int ys2 = (int)p.ys[2], ys3 = (int)p.ys[3];
   int yy = tid / per_row, ci = tid - yy * per_row;
   const int dyy = nthr / per_row, dci = nthr - dyy * per_row;
   for (int i = tid; i < total; i += nthr) {
-    const int pq = ci / nch, ch = ci - pq * nch;
+    const int pq = (nch == 1) ? ci : ci / nch;
+    const int ch = (nch == 1) ? 0 : ci - pq * nch;
     const int xx = 2 * pq;
     const bool two = xx + 1 < nc;
     const T* ss = src + (ch * V) * oplane + (yy * s) * op + xx * s;
     Chunk<T, CB> c0, c1;
+    if (s == 1 && sizeof(T) == 2) {          // two adjacent 16-bit pixels per 32-bit load
 #pragma unroll
-    for (int e = 0; e < V; ++e) c0.set(e, ss[e * oplane]);
-    if (two) {
+      for (int e = 0; e < V; ++e) {
+        Chunk<T, 4> t;
+        t.raw = *reinterpret_cast<const unsigned int*>(ss + e * oplane);
+        c0.set(e, t.get(0)); c1.set(e, t.get(1));
+      }
+    } else {
 #pragma unroll
-      for (int e = 0; e < V; ++e) c1.set(e, ss[e * oplane + s]);
+      for (int e = 0; e < V; ++e) c0.set(e, ss[e * oplane]);
+      if (two) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) c1.set(e, ss[e * oplane + s]);
+      }
     }
-    T* dd = dst + (size_t)yy * p.ys[2] + (size_t)xx * p.ys[3] + ch * V;
-    *reinterpret_cast<typename RawChunk<CB>::type*>(dd) = c0.raw;
-    if (two) *reinterpret_cast<typename RawChunk<CB>::type*>(dd + p.ys[3]) = c1.raw;
+    T* dd = dst + yy * ys2 + xx * ys3 + ch * V;
+    *reinterpret_cast<Raw*>(dd) = c0.raw;
+    if (two) *reinterpret_cast<Raw*>(dd + ys3) = c1.raw;
     yy += dyy; ci += dci;
     if (ci >= per_row) { ci -= per_row; ++yy; }
   }
@@ -476,7 +541,8 @@ WT_HD void store_chunks(const Plan2d& p, T* __restrict__ dst, const T* __restric
 // Any layout: one item = four consecutive output pixels of one channel.
 template <typename T>
 WT_HD void store_planar(const Plan2d& p, T* __restrict__ dst, const T* __restrict__ src, int gc, int nr, int nc,
-                        int op, int oplane, int s, int tid, int nthr) {
+                        int s, int tid, int nthr) {
+  const int op = p.opitch, oplane = p.oplane;
   const int ngrp = (nc + 3) >> 2;
   const int per_g = nr * ngrp;
   const int total = gc * per_g;
@@ -498,14 +564,20 @@ WT_HD void store_planar(const Plan2d& p, T* __restrict__ dst, const T* __restric
 }
 
 // ---------------------------------------------------------------------------
-// The CTA body.  `bid` is the linear block index; x / y are the launch's input
-// and output, `rin` / `rout` fp32 (B,C,h,w)-contiguous planes used by the
-// multi-launch path for planes that do not fit on chip.
+// The CTA body.  `bid` is the linear block index.
+//   FINAL = true : last stage of a layer: reads x (type T), adds the base
+//                  convolution and writes y (type T).  X0 is kept in T when T is
+//                  a 16-bit type.
+//   FINAL = false: deep stage: reads either x (type T, low-pass block sums formed
+//                  while loading) or fp32 planes from scratch (T = float), and
+//                  writes fp32 (B,C,h,w)-contiguous planes of its reconstruction.
+// `rin` / `rout` are the fp32 planes that connect the stages of one layer.
 // ---------------------------------------------------------------------------
-template <typename T, int K>
+template <typename T, int K, bool FINAL>
 WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
                     const float* __restrict__ packed, const float* __restrict__ rin,
                     float* __restrict__ rout, float* smem, int bid) {
+  typedef typename Select<FINAL && sizeof(T) == 2, T, float>::type XT;
   const int nthr = p.nthreads;
   const int d = p.nlev;
   // block -> (channel group, tile x, tile y, sample); the group index runs fastest so
@@ -539,25 +611,25 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         reinterpret_cast<float4*>(smem + p.woff)[i] = src[sk];
       }
     }
-    // input tile -> X0 (fp32); everything the tile does not take from the plane is zero
+    // input tile -> X0; everything the tile does not take from the plane is zero
     FillRange fr;
     fr.ylo = imax(ay.lo[0], 0); fr.yhi = imin(ay.hi[0], p.H);
     fr.xlo = imax(ax.lo[0], 0); fr.xhi = imin(ax.hi[0], p.W);
     fr.orgy = ay.org[0]; fr.orgx = ax.org[0];
     const T* xb = x + (size_t)nb * p.xs[0] + (size_t)c0 * p.xs[1];
-    float* x0arr = smem + p.off[0];
+    XT* x0arr = sm.x0<XT>(0);
     if (p.x_vec && gc == p.G && p.in_shift <= 1) {
-      if (p.in_shift == 0) {
-        if (p.x_vec == 16) fill_x0_chunks<T, 16, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
-        else if (p.x_vec == 8) fill_x0_chunks<T, 8, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
-        else fill_x0_chunks<T, 4, 1>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+      if (FINAL || p.in_shift == 0) {
+        if (p.x_vec == 16) fill_x0_chunks<T, XT, 16, 1>(p, xb, x0arr, fr, tid, nthr);
+        else if (p.x_vec == 8) fill_x0_chunks<T, XT, 8, 1>(p, xb, x0arr, fr, tid, nthr);
+        else fill_x0_chunks<T, XT, 4, 1>(p, xb, x0arr, fr, tid, nthr);
       } else {
-        if (p.x_vec == 16) fill_x0_chunks<T, 16, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
-        else if (p.x_vec == 8) fill_x0_chunks<T, 8, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
-        else fill_x0_chunks<T, 4, 2>(p, xb, x0arr, fr, p.rows[0], p.pitch[0], tid, nthr);
+        if (p.x_vec == 16) fill_x0_chunks<T, XT, 16, 2>(p, xb, x0arr, fr, tid, nthr);
+        else if (p.x_vec == 8) fill_x0_chunks<T, XT, 8, 2>(p, xb, x0arr, fr, tid, nthr);
+        else fill_x0_chunks<T, XT, 4, 2>(p, xb, x0arr, fr, tid, nthr);
       }
     } else {
-      fill_x0_planar<T>(p, xb, x0arr, fr, gc, p.rows[0], p.pitch[0], tid, nthr);
+      fill_x0_planar<T, XT>(p, xb, x0arr, fr, gc, tid, nthr);
     }
     // reconstruction of the deeper levels, produced by an earlier launch
     if (p.has_rin) {
@@ -574,7 +646,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         const int dg = nthr / per_g, drem = nthr - dg * per_g;
         const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
         for (int i = tid; i < total; i += nthr) {
-          const float* rs = rb + (size_t)g * (Hd * Wd) + (size_t)yy * Wd + 4 * gq;
+          const float* rs = rb + (size_t)g * (Hd * Wd) + yy * Wd + 4 * gq;
           float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
           if (vec_ok && 4 * gq + 3 < wn) t = *reinterpret_cast<const float4*>(rs);
           else {
@@ -594,7 +666,10 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
 
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
-    WT_PHASE(nthr) { analysis_level<K>(p, sm, ay, ax, j, gc, tid, nthr); }
+    WT_PHASE(nthr) {
+      if (j == 1) analysis_level<K, XT>(p, sm, ay, ax, 1, sm.x0<XT>(0), p.plane[0], gc, tid, nthr);
+      else analysis_level<K, float>(p, sm, ay, ax, j, sm.sub(j - 1, 0, 0), p.plane[j - 1], gc, tid, nthr);
+    }
   }
 
   // ---- phase 2: deep levels bottom-up: per-sub-band convolutions into Y, then the
@@ -603,12 +678,12 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     WT_PHASE(nthr) {
       const int th = p.th[j];
       const int nty = cdiv(ay.n[j], th), ntx = cdiv(ax.n[j], 4);
-      const int per = nty * ntx;
-      const int total = gc * 4 * per;
+      const int per = gc * 4;
+      const int total = per * nty * ntx;
       for (int i = tid; i < total; i += nthr) {
-        const int t = i % per;
-        const int gs = i / per;
-        const int s = gs & 3, g = gs >> 2;
+        const int t = i / per;
+        const int gs = i - t * per;          // channel fastest, then sub-band, then tile
+        const int s = gs / gc, g = gs - s * gc;
         const int iy = t / ntx, ix = t - iy * ntx;
         if (th == 4) deep_item<K, 4>(p, sm, ay, ax, j, g, s, iy, ix);
         else deep_item<K, 2>(p, sm, ay, ax, j, g, s, iy, ix);
@@ -618,7 +693,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       const int hn = ay.n[j], wn = ax.n[j];
       const int total = gc * hn * wn;
       const bool has_r = (j < d) || p.has_rin;
-      const int yplane = p.yrows * p.ypitch;
+      const int ystep = p.G * p.yplane;
       const int nrow = ay.n[j - 1], ncol = ax.n[j - 1];
       const int opitch = p.rpitch[j - 1];
       for (int i = tid; i < total; i += nthr) {
@@ -629,7 +704,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         float ll = yb[0];
         if (has_r) ll += sm.rec(j, g)[yy * p.rpitch[j] + xx];
         float o00, o01, o10, o11;
-        synth4(ll, yb[yplane], yb[2 * yplane], yb[3 * yplane], o00, o01, o10, o11);
+        synth4(ll, yb[ystep], yb[2 * ystep], yb[3 * ystep], o00, o01, o10, o11);
         float* out = sm.rec(j - 1, g) + (2 * yy) * opitch + 2 * xx;
         const bool c1 = 2 * xx + 1 < ncol;
         out[0] = o00;                                  // (2yy, 2xx) is always inside
@@ -642,38 +717,36 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
-  // ---- phase 3: top level of the stage (+ base convolution and bias)
+  // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
+  //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
     if (d >= 1) {
       const int nty = cdiv(ay.n[1], 2), ntx = cdiv(ax.n[1], 4);
-      const int per = nty * ntx;
-      const int total = gc * per;
+      const int total = gc * nty * ntx;
       const bool has_r = (d > 1) || p.has_rin;
       for (int i = tid; i < total; i += nthr) {
-        const int g = i / per;
-        const int t = i - g * per;
+        const int t = i / gc;
+        const int g = i - t * gc;
         const int iy = t / ntx, ix = t - iy * ntx;
-        if (p.has_base) top_item<T, K, 2, 4, true>(p, sm, ay, ax, g, iy, ix, has_r, out_tile);
-        else top_item<T, K, 2, 4, false>(p, sm, ay, ax, g, iy, ix, has_r, out_tile);
+        top_item<T, XT, K, FINAL>(p, sm, ay, ax, g, iy, ix, has_r, out_tile);
       }
-    } else {
+    } else if (FINAL) {
       const int nty = cdiv(ay.n[0], 4), ntx = cdiv(ax.n[0], 8);
-      const int per = nty * ntx;
-      const int total = gc * per;
+      const int total = gc * nty * ntx;
       for (int i = tid; i < total; i += nthr) {
-        const int g = i / per;
-        const int t = i - g * per;
+        const int t = i / gc;
+        const int g = i - t * gc;
         const int iy = t / ntx, ix = t - iy * ntx;
-        base_item<T, K, 4, 8>(p, sm, ay, ax, g, iy, ix, out_tile);
+        base_item<T, XT, K>(p, sm, ay, ax, g, iy, ix, out_tile);
       }
     }
   }
 
   // ---- phase 4: write the tile
   WT_PHASE(nthr) {
-    if (p.out_planes) {
+    if (!FINAL) {
       const int rp = p.rpitch[0];
-      const int rplane = p.rrows[0] * rp;
+      const int rplane = p.rplane[0];
       const float* r0 = smem + p.roff[0];
       const int hn = ay.n[0], wn = ax.n[0];
       const int ngrp = (wn + 3) >> 2;
@@ -688,7 +761,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
         for (int i = tid; i < total; i += nthr) {
           const float4 t = *reinterpret_cast<const float4*>(r0 + g * rplane + yy * rp + 4 * gq);
-          float* od = ob + (size_t)g * (p.H * p.W) + (size_t)yy * p.W + 4 * gq;
+          float* od = ob + (size_t)g * (p.H * p.W) + yy * p.W + 4 * gq;
           if (vec_ok && 4 * gq + 3 < wn) *reinterpret_cast<float4*>(od) = t;
           else {
             if (4 * gq + 0 < wn) od[0] = t.x;
@@ -702,20 +775,18 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         }
       }
     } else {
-      const int op = p.opitch;
-      const int oplane = p.orows * op;
       const int s = p.out_stride;
       const int oy0 = cdiv(ay.t0, s), oy1 = cdiv(ay.t1, s);
       const int ox0 = cdiv(ax.t0, s), ox1 = cdiv(ax.t1, s);
       const int nr = oy1 - oy0, nc = ox1 - ox0;
       T* yb = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1] + (size_t)oy0 * p.ys[2] + (size_t)ox0 * p.ys[3];
-      const T* o0 = out_tile + (oy0 * s - ay.t0) * op + (ox0 * s - ax.t0);
+      const T* o0 = out_tile + (oy0 * s - ay.t0) * p.opitch + (ox0 * s - ax.t0);
       if (p.y_vec && gc == p.G) {
-        if (p.y_vec == 16) store_chunks<T, 16>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
-        else if (p.y_vec == 8) store_chunks<T, 8>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
-        else store_chunks<T, 4>(p, yb, o0, nr, nc, op, oplane, s, tid, nthr);
+        if (p.y_vec == 16) store_chunks<T, 16>(p, yb, o0, nr, nc, s, tid, nthr);
+        else if (p.y_vec == 8) store_chunks<T, 8>(p, yb, o0, nr, nc, s, tid, nthr);
+        else store_chunks<T, 4>(p, yb, o0, nr, nc, s, tid, nthr);
       } else {
-        store_planar<T>(p, yb, o0, gc, nr, nc, op, oplane, s, tid, nthr);
+        store_planar<T>(p, yb, o0, gc, nr, nc, s, tid, nthr);
       }
     }
   }

@@ -78,36 +78,53 @@ inline long long layout_stage(Plan2d& p) {
       }
     }
   }
+  // Planes are padded so that consecutive channels start 16*(8/min(G,8)) bytes further in
+  // the bank pattern: the lanes of a quarter warp work on different channels of one tile.
+  const int lanes_g = imin(p.G, 8);
+  const int want_words = (lanes_g > 1) ? 4 * (8 / lanes_g) : 0;     // plane size mod 32 words
+  auto pad_words = [&](long long words) {
+    words = (words + 3) / 4 * 4;
+    if (lanes_g > 1) while (words % 32 != want_words) words += 4;
+    return words;
+  };
   long long off = 0;
   p.woff = (int)off;
   p.wsm = p.tapset * (p.has_base + 4 * d);
   off += (long long)p.G * p.wsm;
+  p.x0_bytes = (p.has_base && p.elem_size == 2) ? 2 : 4;
   for (int j = 0; j <= d; ++j) {
     p.rows[j] = ext[0][j];
     p.pitch[j] = round_up(ext[1][j], 4);
     p.off[j] = (int)off;
-    off += (long long)p.G * (j == 0 ? 1 : 4) * p.rows[j] * p.pitch[j];
+    const int esz = (j == 0) ? p.x0_bytes : 4;
+    const long long words = pad_words(((long long)p.rows[j] * p.pitch[j] * esz + 3) / 4);
+    p.plane[j] = (int)(words * 4 / esz);
+    off += (long long)p.G * (j == 0 ? 1 : 4) * words;
   }
   p.yrows = yext[0];
   p.ypitch = round_up(yext[1], 4);
+  p.yplane = (int)pad_words((long long)p.yrows * p.ypitch);
   p.yoff = (int)off;
-  off += (long long)p.G * 4 * p.yrows * p.ypitch;
+  off += (long long)p.G * 4 * p.yplane;
   for (int j = 0; j <= d; ++j) {
     // R_0 only exists in stages without a base convolution (their output); R_d only when
     // an earlier launch provides it
     const bool needed = (j == 0) ? !p.has_base : ((j < d) || p.has_rin);
     p.rrows[j] = needed ? rext[0][j] : 0;
     p.rpitch[j] = needed ? round_up(rext[1][j], 4) : 0;
+    p.rplane[j] = needed ? (int)pad_words((long long)p.rrows[j] * p.rpitch[j]) : 0;
     p.roff[j] = (int)off;
-    off += (long long)p.G * p.rrows[j] * p.rpitch[j];
+    off += (long long)p.G * p.rplane[j];
   }
   p.ooff = (int)off;
-  p.orows = p.opitch = 0;
+  p.orows = p.opitch = p.oplane = 0;
   if (p.has_base) {
     const int tile_y = imin(p.TY, p.H), tile_x = imin(p.TX, p.W);
     p.orows = round_up(tile_y, 4);
     p.opitch = round_up(tile_x, 8);
-    off += ((long long)p.G * p.orows * p.opitch * p.elem_size + 3) / 4;
+    const long long words = pad_words(((long long)p.orows * p.opitch * p.elem_size + 3) / 4);
+    p.oplane = (int)(words * 4 / p.elem_size);
+    off += (long long)p.G * words;
   }
   off += 4;                       // the last window may over-read up to three floats
   off = (off + 3) / 4 * 4;

@@ -47,12 +47,15 @@ struct Plan2d {
   int elem_size;         // bytes per element of T (the launch's input / output type)
   // per-level extents, j = 0 (input plane) .. nlev
   int Hj[kMaxFused + 1], Wj[kMaxFused + 1];
-  int rows[kMaxFused + 1], pitch[kMaxFused + 1], off[kMaxFused + 1];
-  int rrows[kMaxFused + 1], rpitch[kMaxFused + 1], roff[kMaxFused + 1];
+  // arrays of level j: rows x pitch elements per channel (and sub-band), `plane` elements
+  // apart (padded for bank spreading), starting `off` floats into shared memory
+  int rows[kMaxFused + 1], pitch[kMaxFused + 1], plane[kMaxFused + 1], off[kMaxFused + 1];
+  int rrows[kMaxFused + 1], rpitch[kMaxFused + 1], rplane[kMaxFused + 1], roff[kMaxFused + 1];
   int th[kMaxFused + 1], tw[kMaxFused + 1];   // thread tile per level (j=0: base conv tile)
   int woff, wsm;         // staged tap sets: offset, floats per channel
-  int yoff, yrows, ypitch;   // Y scratch of the deep levels (4 sub-band arrays per channel)
-  int ooff, orows, opitch;   // OUT staging tile: offset in floats, rows / pitch in elements of T
+  int yoff, yrows, ypitch, yplane;   // Y scratch of the deep levels (4 sub-band arrays per channel)
+  int ooff, orows, opitch, oplane;   // OUT staging tile: offset in floats; rows / pitch / plane in elements of T
+  int x0_bytes;              // element size of X0: the activation size when 16-bit and final, else 4
   int smem_floats;
   // tensor strides in elements (n,c,h,w)
   long long xs[4], ys[4];
