@@ -37,6 +37,10 @@ extern "C" {
 #define WTCONV_ERR_MISALIGNED (-5)     /* a pointer is not aligned to its element type      */
 #define WTCONV_ERR_TOO_LARGE (-6)      /* a dimension overflows the 32-bit index plan       */
 #define WTCONV_ERR_NO_DEVICE (-7)      /* no usable CUDA device / not an sm_100 device      */
+#define WTCONV_ERR_SCRATCH_LIMIT (-8)  /* problem needs more than WTCONV_STATIC_SCRATCH_BYTES */
+
+/* size of the scratch array built into the library for wtconv2d_forward_noalloc */
+#define WTCONV_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* wtconv_query() selectors */
 #define WTCONV_QUERY_VERSION 0         /* ABI version, currently 1                          */
@@ -120,6 +124,40 @@ int wtconv2d_forward(const void* x, void* y, const float* packed,
                      void* workspace, size_t workspace_bytes,
                      int B, int C, int H, int W, int K, int L, int stride, int dtype,
                      const long long* x_strides, const long long* y_strides, void* stream);
+
+/*
+ * WTConv2d forward for callers that must not allocate device memory.
+ *
+ * Same arguments and result as wtconv2d_forward, minus the workspace: the
+ * scratch planes that large inputs need (see wtconv2d_workspace_bytes) live in
+ * an array of WTCONV_STATIC_SCRATCH_BYTES that is part of the library image, so
+ * neither this call nor its caller runs cudaMalloc / cudaFree or any allocating
+ * library routine.  It is meant for hosts that cannot allocate at call time:
+ * code running inside a CUDA-graph capture or a real-time serving loop where an
+ * allocation would synchronise the device, plug-ins that are handed fixed
+ * buffers by an inference runtime and own no allocator, and embedders whose
+ * memory budget is frozen after start-up.
+ *
+ *   - Problems whose scratch need exceeds WTCONV_STATIC_SCRATCH_BYTES are
+ *     rejected with WTCONV_ERR_SCRATCH_LIMIT before anything is launched (for
+ *     example bf16 channels-last 56x56 planes with 5 levels need B*C*3136 bytes:
+ *     up to B*C = 5349 planes fit).  Problems that need no scratch always pass.
+ *   - Every GPU whose context loads the library holds the array until the
+ *     process exits.
+ *   - The first call on a device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current).  Make that first call
+ *     before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the last
+ *     call left in it.  The kernels overwrite every scratch plane they later
+ *     read, so nothing has to be cleared between calls; but two calls that can
+ *     overlap on the GPU (different streams, no ordering) race on it -- order
+ *     them on one stream or with events.
+ * This entry point has no counterpart in the reference, whose intermediates are
+ * ordinary torch allocations.
+ */
+int wtconv2d_forward_noalloc(const void* x, void* y, const float* packed,
+                             int B, int C, int H, int W, int K, int L, int stride, int dtype,
+                             const long long* x_strides, const long long* y_strides, void* stream);
 
 /*
  * WTConv1d forward, replaces WTConv1d.forward (wtconv/wtconv1d.py:38-87) and

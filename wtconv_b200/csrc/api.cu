@@ -2,6 +2,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/wtconv_b200.h"
 #include "wt1d_host.h"
@@ -109,6 +110,9 @@ const char* wtconv_status_string(int status) {
     case WTCONV_ERR_MISALIGNED: return "a tensor pointer is not aligned to its element size";
     case WTCONV_ERR_TOO_LARGE: return "problem too large for the on-chip plan (dimension or shared-memory limit)";
     case WTCONV_ERR_NO_DEVICE: return "no usable sm_100 CUDA device";
+    case WTCONV_ERR_SCRATCH_LIMIT:
+      return "problem needs more scratch than the library's built-in array (WTCONV_STATIC_SCRATCH_BYTES); "
+             "use wtconv2d_forward with a caller-provided workspace";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
@@ -200,6 +204,59 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     if (e != cudaSuccess) return (int)e;
   }
   return WTCONV_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the scratch planes live in the library image.
+// ---------------------------------------------------------------------------
+namespace {
+
+// Part of every context that loads the library; 256-byte aligned so that the fp32 planes and
+// their 128-bit accesses are aligned whatever the offsets inside it.
+static __device__ __align__(256) unsigned char g_static_scratch[WTCONV_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {nullptr};   // device address of g_static_scratch, per device
+
+// `g_static_scratch` is only a host-side handle here: kernels need the device address, which
+// differs per device.  Looked up once per device, with that device current.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return WTCONV_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!ptr) return WTCONV_ERR_NO_DEVICE;
+    g_scratch_addr[dev] = ptr;
+  }
+  *out = g_scratch_addr[dev];
+  return WTCONV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int wtconv2d_forward_noalloc(const void* x, void* y, const float* packed, int B, int C, int H, int W, int K, int L,
+                             int stride, int dtype, const long long* x_strides, const long long* y_strides,
+                             void* stream) {
+  // size check first: reject before touching the device
+  size_t need = 0;
+  const int st = wtconv2d_workspace_bytes(B, C, H, W, K, L, dtype, x_strides, y_strides, &need);
+  if (st) return st;
+  if (need > (size_t)WTCONV_STATIC_SCRATCH_BYTES) return WTCONV_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  const int sa = static_scratch_address(&scratch);
+  if (sa) return sa;
+  return wtconv2d_forward(x, y, packed, scratch, (size_t)WTCONV_STATIC_SCRATCH_BYTES, B, C, H, W, K, L, stride, dtype,
+                          x_strides, y_strides, stream);
 }
 
 int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, int N, int K, int L, int stride,
