@@ -231,9 +231,8 @@ def run_ours(args):
             barrier()
         ms = e0.elapsed_time(e1)
         if dist is not None:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            from wtconv_b200.sharding import max_over_ranks
+            ms = max_over_ranks(ms, dev)
         return ms / steps
 
     sampler = ClockSampler(local)
@@ -294,7 +293,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": in_bytes},
-        "gpu_launches": 5 * args.steps,
+        "gpu_launches": sum(2 if H > 28 else 1 for _, H, _ in STAGES) * args.steps,
         "clocks": clocks,
     }
     print(json.dumps(line))
@@ -309,8 +308,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=128, help="per-GPU batch (128 = the BASELINE workload; "
+                    "smaller values are for profiler captures)")
+    ap.add_argument("--stages", default="0,1,2,3", help="subset of the four stage layers (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
+    global BATCH, STAGES
+    BATCH = args.batch
+    STAGES = [STAGES[int(i)] for i in args.stages.split(",")]
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
