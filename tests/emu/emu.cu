@@ -29,13 +29,17 @@ struct AlignedBuf {
 template <typename T, int K>
 void run2d(const Plan2d& p, const void* x, void* y, const float* packed, const float* rin, float* rout) {
   AlignedBuf smem(p.smem_floats + 16);
-  const long long blocks = (long long)p.ngroups * p.ntile_x * p.ntile_y * p.B;
-  for (long long b = 0; b < blocks; ++b) {
-    // poison the buffer so that a cell the kernel forgets to clear shows up
-    for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
-    if (p.has_base) wt2d_cta<T, K, true>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
-    else wt2d_cta<T, K, false>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, (int)b);
-  }
+  for (int nb = 0; nb < p.B; ++nb)
+    for (int by = 0; by < p.ntile_y; ++by)
+      for (int bx = 0; bx < p.ntile_x; ++bx)
+        for (int cg = 0; cg < p.ngroups; ++cg) {
+          // poison the buffer so that a cell the kernel forgets to write shows up
+          for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
+          if (p.has_base)
+            wt2d_cta<T, K, true>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, cg, bx, by, nb);
+          else
+            wt2d_cta<T, K, false>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, rin, rout, smem.p, cg, bx, by, nb);
+        }
 }
 
 template <int K>

@@ -70,7 +70,9 @@ int make_layer2d(Layer2d& ly, const void* x, const void* y, int B, int C, int H,
   const int st = check_common(C, K, L, dtype);
   if (st) return st;
   if (B <= 0 || H <= 0 || W <= 0 || stride < 1) return WTCONV_ERR_BAD_ARG;
-  if ((long long)B * C * H * W >= (1LL << 40) || H > (1 << 24) || W > (1 << 24)) return WTCONV_ERR_TOO_LARGE;
+  if ((long long)B * C * H * W >= (1LL << 40) || H > (1 << 20) || W > (1 << 20) || B > 65535 ||
+      (long long)C * H * W >= (1LL << 31))
+    return WTCONV_ERR_TOO_LARGE;   // grid.z carries the sample index; per-sample offsets are 32-bit
   ly.B = B; ly.C = C; ly.H = H; ly.W = W; ly.K = K; ly.L = L; ly.stride = stride;
   ly.elem_size = elem_size(dtype);
   const int Ho = cdiv(H, stride), Wo = cdiv(W, stride);

@@ -133,6 +133,17 @@ WT_HD void synth4(float ll, float lh, float hl, float hh, float& o00, float& o01
   o00 = pp + uu; o01 = pp - uu; o10 = qq + vv; o11 = qq - vv;
 }
 
+// Geometry of the CTA's tile: the two tile ranges plus what level_geo needs.  Levels are
+// evaluated on demand (closed form, registers only).
+struct TileGeo {
+  int d, r, rb;
+  int ty0, ty1, tx0, tx1;
+  const int* Hj;
+  const int* Wj;
+  WT_HD LevelGeo y(int j) const { return level_geo(d, r, rb, j, Hj[j], ty0, ty1, 0); }
+  WT_HD LevelGeo x(int j) const { return level_geo(d, r, rb, j, Wj[j], tx0, tx1, 3); }
+};
+
 // ---------------------------------------------------------------------------
 // Top-level item: 2 x 4 positions of level 1 of this stage for one channel.
 // Four scaled sub-band convolutions, low-pass accumulation of the deeper
@@ -140,17 +151,15 @@ WT_HD void synth4(float ll, float lh, float hl, float hh, float& o00, float& o01
 // block of R_0 in registers.  With FUSE_BASE the base convolution and bias
 // (wtconv2d.py:81-82) are accumulated on top and the finished block goes to the
 // OUT staging tile; otherwise the block is written to R_0 (cropped).
+// (wy1, wx1) / (wy0, wx0): array coordinates of the item's level-1 / level-0 window.
 // ---------------------------------------------------------------------------
 template <typename T, typename XT, int K, bool FUSE_BASE>
-WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int g, int iy, int ix,
-                    bool has_r, T* __restrict__ out_tile) {
+WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, int wy1, int wx1, int wy0, int wx0,
+                    int nrow0, int ncol0, bool has_r, T* __restrict__ out_tile) {
   constexpr int TH = 2, TW = 4;
-  const int r = p.r;
   float acc[2 * TH][2 * TW];
   {
     const int pitch = p.pitch[1];
-    const int wy = ay.a[1] + iy * TH - r - ay.org[1];   // window origin in array coordinates
-    const int wx = ax.a[1] + ix * TW - r - ax.org[1];
     float y[4][TH][TW];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
@@ -158,7 +167,7 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
       for (int i = 0; i < TH; ++i)
 #pragma unroll
         for (int q = 0; q < TW; ++q) y[s][i][q] = 0.f;
-      conv_tile<K, TH, TW, float>(sm.sub(1, g, s) + wy * pitch + wx, pitch, sm.taps(g, 1, s), y[s]);
+      conv_tile<K, TH, TW, float>(sm.sub(1, g, s) + wy1 * pitch + wx1, pitch, sm.taps(g, 1, s), y[s]);
     }
     if (has_r) {
       const float* rj = sm.rec(1, g) + (iy * TH) * p.rpitch[1] + ix * TW;
@@ -178,15 +187,13 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
   }
   if (FUSE_BASE) {
     const int pitch = p.pitch[0];
-    const int wy = ay.t0 + iy * 2 * TH - r - ay.org[0];
-    const int wx = ax.t0 + ix * 2 * TW - r - ax.org[0];
     const float* wts = sm.taps(g, 0, 0);
     const float bias = wts[K * K];
 #pragma unroll
     for (int i = 0; i < 2 * TH; ++i)
 #pragma unroll
       for (int q = 0; q < 2 * TW; ++q) acc[i][q] += bias;
-    conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy * pitch + wx, pitch, wts, acc);
+    conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc);
     // finished pixels -> OUT[g]; the tile is allocated with the overhang of partial items
     T* o = out_tile + g * p.oplane + (iy * 2 * TH) * p.opitch + ix * 2 * TW;
 #pragma unroll
@@ -197,14 +204,13 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
   } else {
     float* out = sm.rec(0, g);
     const int opitch = p.rpitch[0];
-    const int nrow = ay.n[0], ncol = ax.n[0];
 #pragma unroll
     for (int i = 0; i < 2 * TH; ++i) {
       const int oy = iy * 2 * TH + i;
 #pragma unroll
       for (int q = 0; q < 2 * TW; ++q) {
         const int ox = ix * 2 * TW + q;
-        if (oy < nrow && ox < ncol) out[oy * opitch + ox] = acc[i][q];
+        if (oy < nrow0 && ox < ncol0) out[oy * opitch + ox] = acc[i][q];
       }
     }
   }
@@ -212,13 +218,10 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axi
 
 // Base-only layer (no wavelet level in this stage): OUT = bias + base conv.
 template <typename T, typename XT, int K>
-WT_HD void base_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int g, int iy, int ix,
+WT_HD void base_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, int wy0, int wx0,
                      T* __restrict__ out_tile) {
   constexpr int BH = 4, BW = 8;
-  const int r = p.r;
   const int pitch = p.pitch[0];
-  const int wy = ay.t0 + iy * BH - r - ay.org[0];
-  const int wx = ax.t0 + ix * BW - r - ax.org[0];
   const float* wts = sm.taps(g, 0, 0);
   const float bias = wts[K * K];
   float acc[BH][BW];
@@ -226,7 +229,7 @@ WT_HD void base_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
   for (int i = 0; i < BH; ++i)
 #pragma unroll
     for (int q = 0; q < BW; ++q) acc[i][q] = bias;
-  conv_tile<K, BH, BW, XT>(sm.x0<XT>(g) + wy * pitch + wx, pitch, wts, acc);
+  conv_tile<K, BH, BW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc);
   T* o = out_tile + g * p.oplane + (iy * BH) * p.opitch + ix * BW;
 #pragma unroll
   for (int i = 0; i < BH; ++i) {
@@ -237,12 +240,8 @@ WT_HD void base_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
 
 // Deep-level item: one sub-band s of a TH x 4 tile of level j -> Y[s][g]
 template <int K, int TH>
-WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j, int g, int s,
-                     int iy, int ix) {
-  const int r = p.r;
+WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, int j, int g, int s, int iy, int ix, int wy, int wx) {
   const int pitch = p.pitch[j];
-  const int wy = ay.a[j] + iy * TH - r - ay.org[j];
-  const int wx = ax.a[j] + ix * 4 - r - ax.org[j];
   float y[TH][4];
 #pragma unroll
   for (int i = 0; i < TH; ++i)
@@ -255,12 +254,28 @@ WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Ax
 }
 
 // ---------------------------------------------------------------------------
+// Row walker of the staging phases.  A phase moves `nrows` rows of `ncols` items;
+// P2 = 2^shift >= min(ncols, 32) lanes share a row, so thread t starts at row
+// t >> shift, column t & (P2-1), and steps nthr >> shift rows: no division in the
+// loops.  Rows that are flattened (channel, row) pairs are split with one division
+// per thread and phase, then advanced incrementally.
+// ---------------------------------------------------------------------------
+struct RowWalk {
+  int shift, col0, row0, step;
+  WT_HD RowWalk(int ncols, int tid, int nthr) {
+    shift = lane_shift(ncols);
+    col0 = tid & ((1 << shift) - 1);
+    row0 = tid >> shift;
+    step = nthr >> shift;
+  }
+};
+
+// ---------------------------------------------------------------------------
 // Staging of the input tile.  Every cell of the X0 arrays is written: pixels of
 // the plane that the tile needs get their value, everything else (the zero
 // extension of wtconv2d.py:49-51, the 'same' padding, the overhang of partial
-// thread tiles) gets 0 -- so shared memory never has to be cleared.  Work is
-// walked in groups of four consecutive columns with an incremental counter (no
-// division inside the loops) and all global loads of a group are issued before
+// thread tiles) gets 0 -- so shared memory never has to be cleared.  One item is
+// four consecutive columns; all global loads of an item are issued before
 // their first use.
 // ---------------------------------------------------------------------------
 struct FillRange {   // valid source range in plane coordinates and the array origin
@@ -278,85 +293,80 @@ WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, XT* __rest
   constexpr int V = VEC > 0 ? VEC : 1;
   typedef typename RawChunk<CB>::type Raw;
   const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
-  const int nch = p.G / V;
-  const int ngrp = pitch >> 2;
-  const int per_row = ngrp * nch;
-  const int total = rows * per_row;
-  if (tid >= total) return;
+  const int nch = p.G / V;                        // power of two (G and V are)
+  const int nsh = lane_shift(nch);
+  const int ncols = (pitch >> 2) * nch;
   const int xs2 = (int)p.xs[2], xs3 = (int)p.xs[3];
-  int rr = tid / per_row, ci = tid - rr * per_row;
-  const int drr = nthr / per_row, dci = nthr - drr * per_row;
-  for (int i = tid; i < total; i += nthr) {
-    const int gq = (nch == 1) ? ci : ci / nch;
-    const int ch = (nch == 1) ? 0 : ci - gq * nch;
-    const int py = fr.orgy + rr, px0 = fr.orgx + 4 * gq;
+  const RowWalk w(ncols, tid, nthr);
+  for (int rr = w.row0; rr < rows; rr += w.step) {
+    const int py = fr.orgy + rr;
     const bool rowok = py >= fr.ylo && py < fr.yhi;
-    XT* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
-    float v[4][V];
-    if (EDGE == 1) {
-      Chunk<T, CB> c[4];
-      const T* s0 = src + py * xs2 + px0 * xs3 + ch * V;
+    for (int ci = w.col0; ci < ncols; ci += 32) {
+      const int gq = ci >> nsh, ch = ci & (nch - 1);
+      const int px0 = fr.orgx + 4 * gq;
+      XT* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
+      float v[4][V];
+      if (EDGE == 1) {
+        Chunk<T, CB> c[4];
+        const T* s0 = src + py * xs2 + px0 * xs3 + ch * V;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
-        if (ok) c[k].raw = *reinterpret_cast<const Raw*>(s0 + k * xs3);
-        else {
+        for (int k = 0; k < 4; ++k) {
+          const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
+          if (ok) c[k].raw = *reinterpret_cast<const Raw*>(s0 + k * xs3);
+          else {
 #pragma unroll
-          for (int e = 0; e < V; ++e) c[k].set(e, Elem<T>::from_f(0.f));
-        }
-      }
-      if constexpr (sizeof(XT) == 2) {
-        // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          Chunk<T, 8> q;
-          q.set(0, c[0].get(e)); q.set(1, c[1].get(e)); q.set(2, c[2].get(e)); q.set(3, c[3].get(e));
-          *reinterpret_cast<uint2*>(dd + e * plane) = q.raw;
-        }
-        rr += drr; ci += dci;
-        if (ci >= per_row) { ci -= per_row; ++rr; }
-        continue;
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-#pragma unroll
-        for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-#pragma unroll
-        for (int e = 0; e < V; ++e) v[k][e] = 0.f;
-        const int px = px0 + k;
-        if (rowok && px >= fr.xlo && px < fr.xhi) {
-          Chunk<T, CB> c[EDGE * EDGE];
-          bool ok[EDGE * EDGE];
-          const T* s0 = src + (py * EDGE) * xs2 + (px * EDGE) * xs3 + ch * V;
-#pragma unroll
-          for (int b = 0; b < EDGE * EDGE; ++b) {
-            ok[b] = (py * EDGE + b / EDGE) < p.Hsrc && (px * EDGE + b % EDGE) < p.Wsrc;
-            if (ok[b]) c[b].raw = *reinterpret_cast<const Raw*>(s0 + (b / EDGE) * xs2 + (b % EDGE) * xs3);
-          }
-#pragma unroll
-          for (int by = 0; by < EDGE; ++by) {
-            float racc[V];
-#pragma unroll
-            for (int e = 0; e < V; ++e) racc[e] = 0.f;
-#pragma unroll
-            for (int bx = 0; bx < EDGE; ++bx)
-              if (ok[by * EDGE + bx]) {
-#pragma unroll
-                for (int e = 0; e < V; ++e) racc[e] += Elem<T>::to_f(c[by * EDGE + bx].get(e));
-              }
-#pragma unroll
-            for (int e = 0; e < V; ++e) v[k][e] += racc[e];
+            for (int e = 0; e < V; ++e) c[k].set(e, Elem<T>::from_f(0.f));
           }
         }
+        if constexpr (sizeof(XT) == 2) {
+          // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            Chunk<T, 8> q;
+            q.set(0, c[0].get(e)); q.set(1, c[1].get(e)); q.set(2, c[2].get(e)); q.set(3, c[3].get(e));
+            *reinterpret_cast<uint2*>(dd + e * plane) = q.raw;
+          }
+          continue;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) v[k][e] = 0.f;
+          const int px = px0 + k;
+          if (rowok && px >= fr.xlo && px < fr.xhi) {
+            Chunk<T, CB> c[EDGE * EDGE];
+            bool ok[EDGE * EDGE];
+            const T* s0 = src + (py * EDGE) * xs2 + (px * EDGE) * xs3 + ch * V;
+#pragma unroll
+            for (int b = 0; b < EDGE * EDGE; ++b) {
+              ok[b] = (py * EDGE + b / EDGE) < p.Hsrc && (px * EDGE + b % EDGE) < p.Wsrc;
+              if (ok[b]) c[b].raw = *reinterpret_cast<const Raw*>(s0 + (b / EDGE) * xs2 + (b % EDGE) * xs3);
+            }
+#pragma unroll
+            for (int by = 0; by < EDGE; ++by) {
+              float racc[V];
+#pragma unroll
+              for (int e = 0; e < V; ++e) racc[e] = 0.f;
+#pragma unroll
+              for (int bx = 0; bx < EDGE; ++bx)
+                if (ok[by * EDGE + bx]) {
+#pragma unroll
+                  for (int e = 0; e < V; ++e) racc[e] += Elem<T>::to_f(c[by * EDGE + bx].get(e));
+                }
+#pragma unroll
+              for (int e = 0; e < V; ++e) v[k][e] += racc[e];
+            }
+          }
+        }
       }
+#pragma unroll
+      for (int e = 0; e < V; ++e) store4(dd + e * plane, v[0][e], v[1][e], v[2][e], v[3][e]);
     }
-#pragma unroll
-    for (int e = 0; e < V; ++e) store4(dd + e * plane, v[0][e], v[1][e], v[2][e], v[3][e]);
-    rr += drr; ci += dci;
-    if (ci >= per_row) { ci -= per_row; ++rr; }
   }
 }
 
@@ -367,56 +377,56 @@ WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, XT* __rest
                           int gc, int tid, int nthr) {
   const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
   const int ngrp = pitch >> 2;
-  const int per_g = rows * ngrp;
-  const int total = gc * per_g;
-  if (tid >= total) return;
+  const int nrows = gc * rows;
   const int edge = 1 << p.in_shift;
   const bool vec_ok = (edge == 1) && p.xs[3] == 1 && (sizeof(T) == 4) && ((p.xs[2] & 3) == 0) &&
                       ((p.xs[1] & 3) == 0) && ((p.xs[0] & 3) == 0) &&
                       ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-  int g = tid / per_g, rem = tid - g * per_g;
-  int rr = rem / ngrp, gq = rem - rr * ngrp;
-  const int dg = nthr / per_g, drem = nthr - dg * per_g;
-  const int drr = drem / ngrp, dgq = drem - drr * ngrp;
-  for (int i = tid; i < total; i += nthr) {
-    const int py = fr.orgy + rr, px0 = fr.orgx + 4 * gq;
+  const RowWalk w(ngrp, tid, nthr);
+  if (w.row0 >= nrows) return;
+  int g = w.row0 / rows, rr = w.row0 - g * rows;
+  const int dg = w.step / rows, drr = w.step - dg * rows;
+  for (int row = w.row0; row < nrows; row += w.step) {
+    const int py = fr.orgy + rr;
     const bool rowok = py >= fr.ylo && py < fr.yhi;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
     const T* sb = src + (size_t)g * p.xs[1];
-    if (rowok) {
-      if (vec_ok && px0 >= fr.xlo && px0 + 3 < fr.xhi && (px0 & 3) == 0) {
-        const float4 t = *reinterpret_cast<const float4*>(sb + (size_t)py * p.xs[2] + px0);
-        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-      } else if (edge == 1) {
+    for (int gq = w.col0; gq < ngrp; gq += 32) {
+      const int px0 = fr.orgx + 4 * gq;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (rowok) {
+        if (vec_ok && px0 >= fr.xlo && px0 + 3 < fr.xhi && (px0 & 3) == 0) {
+          const float4 t = *reinterpret_cast<const float4*>(sb + (size_t)py * p.xs[2] + px0);
+          v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else if (edge == 1) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (px0 + k >= fr.xlo && px0 + k < fr.xhi)
-            v[k] = Elem<T>::to_f(sb[(size_t)py * p.xs[2] + (size_t)(px0 + k) * p.xs[3]]);
-      } else {
+          for (int k = 0; k < 4; ++k)
+            if (px0 + k >= fr.xlo && px0 + k < fr.xhi)
+              v[k] = Elem<T>::to_f(sb[(size_t)py * p.xs[2] + (size_t)(px0 + k) * p.xs[3]]);
+        } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int px = px0 + k;
-          if (px >= fr.xlo && px < fr.xhi) {
-            float acc = 0.f;
-            for (int by = 0; by < edge; ++by) {
-              const int sy = py * edge + by;
-              if (sy >= p.Hsrc) break;
-              float racc = 0.f;
-              for (int bx = 0; bx < edge; ++bx) {
-                const int sx = px * edge + bx;
-                if (sx >= p.Wsrc) break;
-                racc += Elem<T>::to_f(sb[(size_t)sy * p.xs[2] + (size_t)sx * p.xs[3]]);
+          for (int k = 0; k < 4; ++k) {
+            const int px = px0 + k;
+            if (px >= fr.xlo && px < fr.xhi) {
+              float acc = 0.f;
+              for (int by = 0; by < edge; ++by) {
+                const int sy = py * edge + by;
+                if (sy >= p.Hsrc) break;
+                float racc = 0.f;
+                for (int bx = 0; bx < edge; ++bx) {
+                  const int sx = px * edge + bx;
+                  if (sx >= p.Wsrc) break;
+                  racc += Elem<T>::to_f(sb[(size_t)sy * p.xs[2] + (size_t)sx * p.xs[3]]);
+                }
+                acc += racc;
               }
-              acc += racc;
+              v[k] = acc;
             }
-            v[k] = acc;
           }
         }
       }
+      store4(dst + g * plane + rr * pitch + 4 * gq, v[0], v[1], v[2], v[3]);
     }
-    store4(dst + g * plane + rr * pitch + 4 * gq, v[0], v[1], v[2], v[3]);
-    g += dg; rr += drr; gq += dgq;
-    if (gq >= ngrp) { gq -= ngrp; ++rr; }
+    g += dg; rr += drr;
     if (rr >= rows) { rr -= rows; ++g; }
   }
 }
@@ -426,64 +436,68 @@ WT_HD void fill_x0_planar(const Plan2d& p, const T* __restrict__ src, XT* __rest
 // LL feeds the next level): one item = four consecutive positions of one
 // channel -> four 128-bit stores (LL, LH, HL, HH).  Positions outside the plane,
 // or whose 2x2 source block is not held on chip, are written as zeros.
-// `src0` is the first source plane (channel 0), `splane` the channel stride.
+// `src0` is the first source plane (channel 0), `splane` the channel stride;
+// (oy, ox) / (soy, sox) are the array origins of this level / the source level.
 // ---------------------------------------------------------------------------
 template <int K, typename ST>
-WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, const Axis& ay, const Axis& ax, int j,
+WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, int j, int oy, int ox, int soy, int sox,
                           const ST* __restrict__ src0, int splane, int gc, int tid, int nthr) {
   const int rows = p.rows[j], pitch = p.pitch[j];
   const int ngrp = pitch >> 2;
-  const int per_g = rows * ngrp;
-  const int total = gc * per_g;
-  if (tid >= total) return;
+  const int nrows = gc * rows;
   const int sp = p.pitch[j - 1], srows = p.rows[j - 1];
   const int dstep = p.G * p.plane[j];                    // distance between sub-band groups
   const int Hj = p.Hj[j], Wj = p.Wj[j];
-  int g = tid / per_g, rem = tid - g * per_g;
-  int rr = rem / ngrp, gq = rem - rr * ngrp;
-  const int dg = nthr / per_g, drem = nthr - dg * per_g;
-  const int drr = drem / ngrp, dgq = drem - drr * ngrp;
-  for (int i = tid; i < total; i += nthr) {
-    const int py = ay.org[j] + rr, px0 = ax.org[j] + 4 * gq;
-    const int sy = 2 * py - ay.org[j - 1], sx0 = 2 * px0 - ax.org[j - 1];
-    float o[4][4];
+  const RowWalk w(ngrp, tid, nthr);
+  if (w.row0 >= nrows) return;
+  int g = w.row0 / rows, rr = w.row0 - g * rows;
+  const int dg = w.step / rows, drr = w.step - dg * rows;
+  for (int row = w.row0; row < nrows; row += w.step) {
+    const int py = oy + rr;
+    const int sy = 2 * py - soy;
+    const bool rowok = py >= 0 && py < Hj && sy >= 0 && sy + 1 < srows;
+    const ST* s0 = src0 + g * splane + sy * sp;
+    float* orow = sm.sub(j, g, 0) + rr * pitch;
+    for (int gq = w.col0; gq < ngrp; gq += 32) {
+      const int px0 = ox + 4 * gq;
+      const int sx0 = 2 * px0 - sox;
+      float o[4][4];
 #pragma unroll
-    for (int s = 0; s < 4; ++s)
+      for (int s = 0; s < 4; ++s)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) o[s][k] = 0.f;
-    if (py >= 0 && py < Hj && sy >= 0 && sy + 1 < srows) {
-      const ST* s0 = src0 + g * splane + sy * sp;
-      float a[8], b[8];
-      const bool full = px0 >= 0 && px0 + 3 < Wj && sx0 >= 0 && sx0 + 7 < sp;
-      if (full && ((K / 2) % 2 == 0)) {          // even radius: source column pairs are aligned
+        for (int k = 0; k < 4; ++k) o[s][k] = 0.f;
+      if (rowok) {
+        float a[8], b[8];
+        const bool full = px0 >= 0 && px0 + 3 < Wj && sx0 >= 0 && sx0 + 7 < sp;
+        if (full && ((K / 2) % 2 == 0)) {          // even radius: source column pairs are aligned
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            load2(s0 + sx0 + 2 * k, a[2 * k], a[2 * k + 1]);
+            load2(s0 + sp + sx0 + 2 * k, b[2 * k], b[2 * k + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int px = px0 + k, sx = sx0 + 2 * k;
+            const bool ok = px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
+            a[2 * k] = ok ? Elem<ST>::to_f(s0[sx]) : 0.f;
+            a[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sx + 1]) : 0.f;
+            b[2 * k] = ok ? Elem<ST>::to_f(s0[sp + sx]) : 0.f;
+            b[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sp + sx + 1]) : 0.f;
+          }
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          load2(s0 + sx0 + 2 * k, a[2 * k], a[2 * k + 1]);
-          load2(s0 + sp + sx0 + 2 * k, b[2 * k], b[2 * k + 1]);
-        }
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int px = px0 + k, sx = sx0 + 2 * k;
-          const bool ok = px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
-          a[2 * k] = ok ? Elem<ST>::to_f(s0[sx]) : 0.f;
-          a[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sx + 1]) : 0.f;
-          b[2 * k] = ok ? Elem<ST>::to_f(s0[sp + sx]) : 0.f;
-          b[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sp + sx + 1]) : 0.f;
+          const float ab = a[2 * k] + a[2 * k + 1], cd = b[2 * k] + b[2 * k + 1];
+          const float amb = a[2 * k] - a[2 * k + 1], cmd = b[2 * k] - b[2 * k + 1];
+          o[0][k] = ab + cd; o[1][k] = ab - cd; o[2][k] = amb + cmd; o[3][k] = amb - cmd;
         }
       }
+      float* od = orow + 4 * gq;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float ab = a[2 * k] + a[2 * k + 1], cd = b[2 * k] + b[2 * k + 1];
-        const float amb = a[2 * k] - a[2 * k + 1], cmd = b[2 * k] - b[2 * k + 1];
-        o[0][k] = ab + cd; o[1][k] = ab - cd; o[2][k] = amb + cmd; o[3][k] = amb - cmd;
-      }
+      for (int s = 0; s < 4; ++s) store4(od + s * dstep, o[s][0], o[s][1], o[s][2], o[s][3]);
     }
-    float* od = sm.sub(j, g, 0) + rr * pitch + 4 * gq;
-#pragma unroll
-    for (int s = 0; s < 4; ++s) store4(od + s * dstep, o[s][0], o[s][1], o[s][2], o[s][3]);
-    g += dg; rr += drr; gq += dgq;
-    if (gq >= ngrp) { gq -= ngrp; ++rr; }
+    g += dg; rr += drr;
     if (rr >= rows) { rr -= rows; ++g; }
   }
 }
@@ -501,40 +515,36 @@ WT_HD void store_chunks(const Plan2d& p, T* __restrict__ dst, const T* __restric
   typedef typename RawChunk<CB>::type Raw;
   const int op = p.opitch, oplane = p.oplane;
   const int nch = p.G / V;
-  const int npair = (nc + 1) >> 1;
-  const int per_row = npair * nch;
-  const int total = nr * per_row;
-  if (tid >= total) return;
+  const int nsh = lane_shift(nch);
+  const int ncols = ((nc + 1) >> 1) * nch;
   const int ys2 = (int)p.ys[2], ys3 = (int)p.ys[3];
-  int yy = tid / per_row, ci = tid - yy * per_row;
-  const int dyy = nthr / per_row, dci = nthr - dyy * per_row;
-  for (int i = tid; i < total; i += nthr) {
-    const int pq = (nch == 1) ? ci : ci / nch;
-    const int ch = (nch == 1) ? 0 : ci - pq * nch;
-    const int xx = 2 * pq;
-    const bool two = xx + 1 < nc;
-    const T* ss = src + (ch * V) * oplane + (yy * s) * op + xx * s;
-    Chunk<T, CB> c0, c1;
-    if (s == 1 && sizeof(T) == 2) {          // two adjacent 16-bit pixels per 32-bit load
+  const RowWalk w(ncols, tid, nthr);
+  for (int yy = w.row0; yy < nr; yy += w.step) {
+    for (int ci = w.col0; ci < ncols; ci += 32) {
+      const int pq = ci >> nsh, ch = ci & (nch - 1);
+      const int xx = 2 * pq;
+      const bool two = xx + 1 < nc;
+      const T* ss = src + (ch * V) * oplane + (yy * s) * op + xx * s;
+      Chunk<T, CB> c0, c1;
+      if (s == 1 && sizeof(T) == 2) {          // two adjacent 16-bit pixels per 32-bit load
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        Chunk<T, 4> t;
-        t.raw = *reinterpret_cast<const unsigned int*>(ss + e * oplane);
-        c0.set(e, t.get(0)); c1.set(e, t.get(1));
+        for (int e = 0; e < V; ++e) {
+          Chunk<T, 4> t;
+          t.raw = *reinterpret_cast<const unsigned int*>(ss + e * oplane);
+          c0.set(e, t.get(0)); c1.set(e, t.get(1));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) c0.set(e, ss[e * oplane]);
+        if (two) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) c1.set(e, ss[e * oplane + s]);
+        }
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < V; ++e) c0.set(e, ss[e * oplane]);
-      if (two) {
-#pragma unroll
-        for (int e = 0; e < V; ++e) c1.set(e, ss[e * oplane + s]);
-      }
+      T* dd = dst + yy * ys2 + xx * ys3 + ch * V;
+      *reinterpret_cast<Raw*>(dd) = c0.raw;
+      if (two) *reinterpret_cast<Raw*>(dd + ys3) = c1.raw;
     }
-    T* dd = dst + yy * ys2 + xx * ys3 + ch * V;
-    *reinterpret_cast<Raw*>(dd) = c0.raw;
-    if (two) *reinterpret_cast<Raw*>(dd + ys3) = c1.raw;
-    yy += dyy; ci += dci;
-    if (ci >= per_row) { ci -= per_row; ++yy; }
   }
 }
 
@@ -544,27 +554,68 @@ WT_HD void store_planar(const Plan2d& p, T* __restrict__ dst, const T* __restric
                         int s, int tid, int nthr) {
   const int op = p.opitch, oplane = p.oplane;
   const int ngrp = (nc + 3) >> 2;
-  const int per_g = nr * ngrp;
-  const int total = gc * per_g;
-  if (tid >= total) return;
-  int g = tid / per_g, rem = tid - g * per_g;
-  int yy = rem / ngrp, gq = rem - yy * ngrp;
-  const int dg = nthr / per_g, drem = nthr - dg * per_g;
-  const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
-  for (int i = tid; i < total; i += nthr) {
-    const T* ss = src + g * oplane + (yy * s) * op + (4 * gq) * s;
-    T* dd = dst + (size_t)g * p.ys[1] + (size_t)yy * p.ys[2] + (size_t)(4 * gq) * p.ys[3];
+  const int nrows = gc * nr;
+  const RowWalk w(ngrp, tid, nthr);
+  if (w.row0 >= nrows) return;
+  int g = w.row0 / nr, yy = w.row0 - g * nr;
+  const int dg = w.step / nr, dyy = w.step - dg * nr;
+  for (int row = w.row0; row < nrows; row += w.step) {
+    for (int gq = w.col0; gq < ngrp; gq += 32) {
+      const T* ss = src + g * oplane + (yy * s) * op + (4 * gq) * s;
+      T* dd = dst + (size_t)g * p.ys[1] + (size_t)yy * p.ys[2] + (size_t)(4 * gq) * p.ys[3];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      if (4 * gq + k < nc) dd[(size_t)k * p.ys[3]] = ss[k * s];
-    g += dg; yy += dyy; gq += dgq;
-    if (gq >= ngrp) { gq -= ngrp; ++yy; }
+      for (int k = 0; k < 4; ++k)
+        if (4 * gq + k < nc) dd[(size_t)k * p.ys[3]] = ss[k * s];
+    }
+    g += dg; yy += dyy;
+    if (yy >= nr) { yy -= nr; ++g; }
+  }
+}
+
+// fp32 plane rows between global memory and shared memory (R_in load, deep-stage output):
+// `nrows` flattened (channel, row) pairs of `ncols` floats, 128-bit when `vec_ok`.
+template <bool LOAD>
+WT_HD void move_plane_rows(float* __restrict__ gmem, int gplane, int gpitch, float* __restrict__ smem_arr,
+                           int splane, int spitch, int gc, int nr, int nc, bool vec_ok, int tid, int nthr) {
+  const int ngrp = (nc + 3) >> 2;
+  const int nrows = gc * nr;
+  const RowWalk w(ngrp, tid, nthr);
+  if (w.row0 >= nrows) return;
+  int g = w.row0 / nr, yy = w.row0 - g * nr;
+  const int dg = w.step / nr, dyy = w.step - dg * nr;
+  for (int row = w.row0; row < nrows; row += w.step) {
+    for (int gq = w.col0; gq < ngrp; gq += 32) {
+      float* gp = gmem + (size_t)g * gplane + (size_t)yy * gpitch + 4 * gq;
+      float* sp = smem_arr + g * splane + yy * spitch + 4 * gq;
+      const bool whole = vec_ok && 4 * gq + 3 < nc;
+      if (LOAD) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (whole) t = *reinterpret_cast<const float4*>(gp);
+        else {
+          if (4 * gq + 0 < nc) t.x = gp[0];
+          if (4 * gq + 1 < nc) t.y = gp[1];
+          if (4 * gq + 2 < nc) t.z = gp[2];
+          if (4 * gq + 3 < nc) t.w = gp[3];
+        }
+        *reinterpret_cast<float4*>(sp) = t;
+      } else {
+        const float4 t = *reinterpret_cast<const float4*>(sp);
+        if (whole) *reinterpret_cast<float4*>(gp) = t;
+        else {
+          if (4 * gq + 0 < nc) gp[0] = t.x;
+          if (4 * gq + 1 < nc) gp[1] = t.y;
+          if (4 * gq + 2 < nc) gp[2] = t.z;
+          if (4 * gq + 3 < nc) gp[3] = t.w;
+        }
+      }
+    }
+    g += dg; yy += dyy;
     if (yy >= nr) { yy -= nr; ++g; }
   }
 }
 
 // ---------------------------------------------------------------------------
-// The CTA body.  `bid` is the linear block index.
+// The CTA body for block (channel group cg, tile bx/by, sample nb).
 //   FINAL = true : last stage of a layer: reads x (type T), adds the base
 //                  convolution and writes y (type T).  X0 is kept in T when T is
 //                  a 16-bit type.
@@ -576,24 +627,19 @@ WT_HD void store_planar(const Plan2d& p, T* __restrict__ dst, const T* __restric
 template <typename T, int K, bool FINAL>
 WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
                     const float* __restrict__ packed, const float* __restrict__ rin,
-                    float* __restrict__ rout, float* smem, int bid) {
+                    float* __restrict__ rout, float* smem, int cg, int bx, int by, int nb) {
   typedef typename Select<FINAL && sizeof(T) == 2, T, float>::type XT;
   const int nthr = p.nthreads;
   const int d = p.nlev;
-  // block -> (channel group, tile x, tile y, sample); the group index runs fastest so
-  // that CTAs sharing the 32-byte sectors of a channels-last pixel are scheduled together
-  const int cg = bid % p.ngroups;
-  int rest = bid / p.ngroups;
-  const int bx = rest % p.ntile_x;
-  rest /= p.ntile_x;
-  const int by = rest % p.ntile_y;
-  const int nb = rest / p.ntile_y;
   const int c0 = cg * p.G;
   const int gc = imin(p.G, p.C - c0);   // channels actually present in this group
+  const int gsh = p.g_shift;            // log2(G) when G is a power of two, else -1
 
-  Axis ay, ax;
-  axis_geometry(d, p.r, p.rb, p.has_base, p.Hj, by * p.TY, imin(p.H, (by + 1) * p.TY), 1, ay);
-  axis_geometry(d, p.r, p.rb, p.has_base, p.Wj, bx * p.TX, imin(p.W, (bx + 1) * p.TX), 4, ax);
+  TileGeo tg;
+  tg.d = d; tg.r = p.r; tg.rb = p.rb;
+  tg.ty0 = by * p.TY; tg.ty1 = imin(p.H, tg.ty0 + p.TY);
+  tg.tx0 = bx * p.TX; tg.tx1 = imin(p.W, tg.tx0 + p.TX);
+  tg.Hj = p.Hj; tg.Wj = p.Wj;
   Smem2d sm{smem, &p};
   T* out_tile = reinterpret_cast<T*>(smem + p.ooff);
 
@@ -601,21 +647,22 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   WT_PHASE(nthr) {
     {
       // per channel: [base set (if any)] [4 sets per level of this stage]
-      const int per = p.wsm / 4;                       // float4 per channel in shared memory
-      const int nbase = p.has_base ? p.tapset / 4 : 0;
-      const int total = gc * per;
-      for (int i = tid; i < total; i += nthr) {
-        const int g = i / per, k = i - g * per;
+      const int per = p.wsm >> 2;                      // float4 per channel in shared memory
+      const int nbase = p.has_base ? (p.tapset >> 2) : 0;
+      const int skip = (p.tapset >> 2) * (1 + 4 * p.lvl0) - nbase;
+      const RowWalk w(per, tid, nthr);
+      for (int g = w.row0; g < gc; g += w.step) {
         const float4* src = reinterpret_cast<const float4*>(packed + (size_t)(c0 + g) * p.wstride);
-        const int sk = (k < nbase) ? k : (p.tapset / 4) * (1 + 4 * p.lvl0) + (k - nbase);
-        reinterpret_cast<float4*>(smem + p.woff)[i] = src[sk];
+        float4* dst = reinterpret_cast<float4*>(smem + p.woff + g * p.wsm);
+        for (int k = w.col0; k < per; k += 32) dst[k] = src[k < nbase ? k : k + skip];
       }
     }
     // input tile -> X0; everything the tile does not take from the plane is zero
+    const LevelGeo gy = tg.y(0), gx = tg.x(0);
     FillRange fr;
-    fr.ylo = imax(ay.lo[0], 0); fr.yhi = imin(ay.hi[0], p.H);
-    fr.xlo = imax(ax.lo[0], 0); fr.xhi = imin(ax.hi[0], p.W);
-    fr.orgy = ay.org[0]; fr.orgx = ax.org[0];
+    fr.ylo = imax(gy.lo, 0); fr.yhi = imin(gy.hi, p.H);
+    fr.xlo = imax(gx.lo, 0); fr.xhi = imin(gx.hi, p.W);
+    fr.orgy = gy.org; fr.orgx = gx.org;
     const T* xb = x + (size_t)nb * p.xs[0] + (size_t)c0 * p.xs[1];
     XT* x0arr = sm.x0<XT>(0);
     if (p.x_vec && gc == p.G && p.in_shift <= 1) {
@@ -633,42 +680,21 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
     // reconstruction of the deeper levels, produced by an earlier launch
     if (p.has_rin) {
-      const int hn = ay.n[d], wn = ax.n[d];
+      const LevelGeo dy = tg.y(d), dx = tg.x(d);
       const int Hd = p.Hj[d], Wd = p.Wj[d];
-      const int ngrp = (wn + 3) >> 2;
-      const int per_g = hn * ngrp;
-      const int total = gc * per_g;
-      const float* rb = rin + ((size_t)nb * p.C + c0) * (size_t)(Hd * Wd) + (size_t)ay.a[d] * Wd + ax.a[d];
-      const bool vec_ok = ((Wd & 3) == 0) && ((ax.a[d] & 3) == 0) && ((Hd * Wd) % 4 == 0);
-      if (tid < total) {
-        int g = tid / per_g, rem = tid - g * per_g;
-        int yy = rem / ngrp, gq = rem - yy * ngrp;
-        const int dg = nthr / per_g, drem = nthr - dg * per_g;
-        const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
-        for (int i = tid; i < total; i += nthr) {
-          const float* rs = rb + (size_t)g * (Hd * Wd) + yy * Wd + 4 * gq;
-          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (vec_ok && 4 * gq + 3 < wn) t = *reinterpret_cast<const float4*>(rs);
-          else {
-            if (4 * gq + 0 < wn) t.x = rs[0];
-            if (4 * gq + 1 < wn) t.y = rs[1];
-            if (4 * gq + 2 < wn) t.z = rs[2];
-            if (4 * gq + 3 < wn) t.w = rs[3];
-          }
-          *reinterpret_cast<float4*>(sm.rec(d, g) + yy * p.rpitch[d] + 4 * gq) = t;
-          g += dg; yy += dyy; gq += dgq;
-          if (gq >= ngrp) { gq -= ngrp; ++yy; }
-          if (yy >= hn) { yy -= hn; ++g; }
-        }
-      }
+      float* rb = const_cast<float*>(rin) + ((size_t)nb * p.C + c0) * (size_t)(Hd * Wd) + (size_t)dy.a * Wd + dx.a;
+      const bool vec_ok = ((Wd & 3) == 0) && ((dx.a & 3) == 0) && (((Hd * Wd) & 3) == 0);
+      move_plane_rows<true>(rb, Hd * Wd, Wd, smem + p.roff[d], p.rplane[d], p.rpitch[d], gc, dy.n, dx.n, vec_ok,
+                            tid, nthr);
     }
   }
 
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
     WT_PHASE(nthr) {
-      if (j == 1) analysis_level<K, XT>(p, sm, ay, ax, 1, sm.x0<XT>(0), p.plane[0], gc, tid, nthr);
-      else analysis_level<K, float>(p, sm, ay, ax, j, sm.sub(j - 1, 0, 0), p.plane[j - 1], gc, tid, nthr);
+      const int oy = tg.y(j).org, ox = tg.x(j).org, soy = tg.y(j - 1).org, sox = tg.x(j - 1).org;
+      if (j == 1) analysis_level<K, XT>(p, sm, 1, oy, ox, soy, sox, sm.x0<XT>(0), p.plane[0], gc, tid, nthr);
+      else analysis_level<K, float>(p, sm, j, oy, ox, soy, sox, sm.sub(j - 1, 0, 0), p.plane[j - 1], gc, tid, nthr);
     }
   }
 
@@ -676,42 +702,55 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   //      low-pass accumulation and synthesis butterfly into R_{j-1}
   for (int j = d; j >= 2; --j) {
     WT_PHASE(nthr) {
+      const LevelGeo ly = tg.y(j), lx = tg.x(j);
       const int th = p.th[j];
-      const int nty = cdiv(ay.n[j], th), ntx = cdiv(ax.n[j], 4);
-      const int per = gc * 4;
+      const int nty = cdiv(ly.n, th), ntx = cdiv(lx.n, 4);
+      const int wy_base = ly.a - p.r - ly.org, wx_base = lx.a - p.r - lx.org;
+      const int per = p.G * 4;                 // channel fastest, then sub-band, then tile
       const int total = per * nty * ntx;
       for (int i = tid; i < total; i += nthr) {
-        const int t = i / per;
-        const int gs = i - t * per;          // channel fastest, then sub-band, then tile
-        const int s = gs / gc, g = gs - s * gc;
+        int t, gs;
+        if (gsh >= 0) { t = i >> (gsh + 2); gs = i & (per - 1); }
+        else { t = i / per; gs = i - t * per; }
+        int s, g;
+        if (gsh >= 0) { s = gs >> gsh; g = gs & (p.G - 1); }
+        else { s = gs / p.G; g = gs - s * p.G; }
+        if (g >= gc) continue;
         const int iy = t / ntx, ix = t - iy * ntx;
-        if (th == 4) deep_item<K, 4>(p, sm, ay, ax, j, g, s, iy, ix);
-        else deep_item<K, 2>(p, sm, ay, ax, j, g, s, iy, ix);
+        if (th == 4) deep_item<K, 4>(p, sm, j, g, s, iy, ix, wy_base + iy * 4, wx_base + ix * 4);
+        else deep_item<K, 2>(p, sm, j, g, s, iy, ix, wy_base + iy * 2, wx_base + ix * 4);
       }
     }
     WT_PHASE(nthr) {
-      const int hn = ay.n[j], wn = ax.n[j];
-      const int total = gc * hn * wn;
+      const LevelGeo ly = tg.y(j), lx = tg.x(j);
+      const int hn = ly.n, wn = lx.n;
       const bool has_r = (j < d) || p.has_rin;
       const int ystep = p.G * p.yplane;
-      const int nrow = ay.n[j - 1], ncol = ax.n[j - 1];
+      const int nrow = tg.y(j - 1).n, ncol = tg.x(j - 1).n;
       const int opitch = p.rpitch[j - 1];
-      for (int i = tid; i < total; i += nthr) {
-        const int xx = i % wn;
-        const int t = i / wn;
-        const int yy = t % hn, g = t / hn;
-        const float* yb = sm.ybuf(g, 0) + yy * p.ypitch + xx;
-        float ll = yb[0];
-        if (has_r) ll += sm.rec(j, g)[yy * p.rpitch[j] + xx];
-        float o00, o01, o10, o11;
-        synth4(ll, yb[ystep], yb[2 * ystep], yb[3 * ystep], o00, o01, o10, o11);
-        float* out = sm.rec(j - 1, g) + (2 * yy) * opitch + 2 * xx;
-        const bool c1 = 2 * xx + 1 < ncol;
-        out[0] = o00;                                  // (2yy, 2xx) is always inside
-        if (c1) out[1] = o01;
-        if (2 * yy + 1 < nrow) {
-          out[opitch] = o10;
-          if (c1) out[opitch + 1] = o11;
+      const int nrows = gc * hn;
+      const RowWalk w(wn, tid, nthr);
+      if (w.row0 < nrows) {
+        int g = w.row0 / hn, yy = w.row0 - g * hn;
+        const int dg = w.step / hn, dyy = w.step - dg * hn;
+        for (int row = w.row0; row < nrows; row += w.step) {
+          for (int xx = w.col0; xx < wn; xx += 32) {
+            const float* yb = sm.ybuf(g, 0) + yy * p.ypitch + xx;
+            float ll = yb[0];
+            if (has_r) ll += sm.rec(j, g)[yy * p.rpitch[j] + xx];
+            float o00, o01, o10, o11;
+            synth4(ll, yb[ystep], yb[2 * ystep], yb[3 * ystep], o00, o01, o10, o11);
+            float* out = sm.rec(j - 1, g) + (2 * yy) * opitch + 2 * xx;
+            const bool c1 = 2 * xx + 1 < ncol;
+            out[0] = o00;                                  // (2yy, 2xx) is always inside
+            if (c1) out[1] = o01;
+            if (2 * yy + 1 < nrow) {
+              out[opitch] = o10;
+              if (c1) out[opitch + 1] = o11;
+            }
+          }
+          g += dg; yy += dyy;
+          if (yy >= hn) { yy -= hn; ++g; }
         }
       }
     }
@@ -720,67 +759,53 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
+    const LevelGeo y0 = tg.y(0), x0g = tg.x(0);
     if (d >= 1) {
-      const int nty = cdiv(ay.n[1], 2), ntx = cdiv(ax.n[1], 4);
-      const int total = gc * nty * ntx;
+      const LevelGeo y1 = tg.y(1), x1 = tg.x(1);
+      const int nty = cdiv(y1.n, 2), ntx = cdiv(x1.n, 4);
+      const int total = p.G * nty * ntx;
       const bool has_r = (d > 1) || p.has_rin;
+      const int wy1 = y1.a - p.r - y1.org, wx1 = x1.a - p.r - x1.org;
+      const int wy0 = y0.a - p.r - y0.org, wx0 = x0g.a - p.r - x0g.org;
       for (int i = tid; i < total; i += nthr) {
-        const int t = i / gc;
-        const int g = i - t * gc;
+        int t, g;
+        if (gsh >= 0) { t = i >> gsh; g = i & (p.G - 1); }
+        else { t = i / p.G; g = i - t * p.G; }
+        if (g >= gc) continue;
         const int iy = t / ntx, ix = t - iy * ntx;
-        top_item<T, XT, K, FINAL>(p, sm, ay, ax, g, iy, ix, has_r, out_tile);
+        top_item<T, XT, K, FINAL>(p, sm, g, iy, ix, wy1 + iy * 2, wx1 + ix * 4, wy0 + iy * 4, wx0 + ix * 8,
+                                  y0.n, x0g.n, has_r, out_tile);
       }
     } else if (FINAL) {
-      const int nty = cdiv(ay.n[0], 4), ntx = cdiv(ax.n[0], 8);
-      const int total = gc * nty * ntx;
+      const int nty = cdiv(y0.n, 4), ntx = cdiv(x0g.n, 8);
+      const int total = p.G * nty * ntx;
+      const int wy0 = y0.a - p.r - y0.org, wx0 = x0g.a - p.r - x0g.org;
       for (int i = tid; i < total; i += nthr) {
-        const int t = i / gc;
-        const int g = i - t * gc;
+        int t, g;
+        if (gsh >= 0) { t = i >> gsh; g = i & (p.G - 1); }
+        else { t = i / p.G; g = i - t * p.G; }
+        if (g >= gc) continue;
         const int iy = t / ntx, ix = t - iy * ntx;
-        base_item<T, XT, K>(p, sm, ay, ax, g, iy, ix, out_tile);
+        base_item<T, XT, K>(p, sm, g, iy, ix, wy0 + iy * 4, wx0 + ix * 8, out_tile);
       }
     }
   }
 
   // ---- phase 4: write the tile
   WT_PHASE(nthr) {
+    const int hn = tg.ty1 - tg.ty0, wn = tg.tx1 - tg.tx0;
     if (!FINAL) {
-      const int rp = p.rpitch[0];
-      const int rplane = p.rplane[0];
-      const float* r0 = smem + p.roff[0];
-      const int hn = ay.n[0], wn = ax.n[0];
-      const int ngrp = (wn + 3) >> 2;
-      const int per_g = hn * ngrp;
-      const int total = gc * per_g;
-      float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)ay.t0 * p.W + ax.t0;
-      const bool vec_ok = ((p.W & 3) == 0) && ((ax.t0 & 3) == 0) && ((p.H * p.W) % 4 == 0);
-      if (tid < total) {
-        int g = tid / per_g, rem = tid - g * per_g;
-        int yy = rem / ngrp, gq = rem - yy * ngrp;
-        const int dg = nthr / per_g, drem = nthr - dg * per_g;
-        const int dyy = drem / ngrp, dgq = drem - dyy * ngrp;
-        for (int i = tid; i < total; i += nthr) {
-          const float4 t = *reinterpret_cast<const float4*>(r0 + g * rplane + yy * rp + 4 * gq);
-          float* od = ob + (size_t)g * (p.H * p.W) + yy * p.W + 4 * gq;
-          if (vec_ok && 4 * gq + 3 < wn) *reinterpret_cast<float4*>(od) = t;
-          else {
-            if (4 * gq + 0 < wn) od[0] = t.x;
-            if (4 * gq + 1 < wn) od[1] = t.y;
-            if (4 * gq + 2 < wn) od[2] = t.z;
-            if (4 * gq + 3 < wn) od[3] = t.w;
-          }
-          g += dg; yy += dyy; gq += dgq;
-          if (gq >= ngrp) { gq -= ngrp; ++yy; }
-          if (yy >= hn) { yy -= hn; ++g; }
-        }
-      }
+      float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)tg.ty0 * p.W + tg.tx0;
+      const bool vec_ok = ((p.W & 3) == 0) && ((tg.tx0 & 3) == 0) && (((p.H * p.W) & 3) == 0);
+      move_plane_rows<false>(ob, p.H * p.W, p.W, smem + p.roff[0], p.rplane[0], p.rpitch[0], gc, hn, wn, vec_ok,
+                             tid, nthr);
     } else {
       const int s = p.out_stride;
-      const int oy0 = cdiv(ay.t0, s), oy1 = cdiv(ay.t1, s);
-      const int ox0 = cdiv(ax.t0, s), ox1 = cdiv(ax.t1, s);
+      const int oy0 = cdiv(tg.ty0, s), oy1 = cdiv(tg.ty1, s);
+      const int ox0 = cdiv(tg.tx0, s), ox1 = cdiv(tg.tx1, s);
       const int nr = oy1 - oy0, nc = ox1 - ox0;
       T* yb = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1] + (size_t)oy0 * p.ys[2] + (size_t)ox0 * p.ys[3];
-      const T* o0 = out_tile + (oy0 * s - ay.t0) * p.opitch + (ox0 * s - ax.t0);
+      const T* o0 = out_tile + (oy0 * s - tg.ty0) * p.opitch + (ox0 * s - tg.tx0);
       if (p.y_vec && gc == p.G) {
         if (p.y_vec == 16) store_chunks<T, 16>(p, yb, o0, nr, nc, s, tid, nthr);
         else if (p.y_vec == 8) store_chunks<T, 8>(p, yb, o0, nr, nc, s, tid, nthr);

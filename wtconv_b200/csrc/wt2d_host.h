@@ -45,6 +45,8 @@ inline long long layout_stage(Plan2d& p) {
   p.ntile_y = cdiv(p.H, p.TY);
   p.ntile_x = cdiv(p.W, p.TX);
   p.ngroups = cdiv(p.C, p.G);
+  p.g_shift = -1;
+  for (int k = 0; k < 8; ++k) if ((1 << k) == p.G) p.g_shift = k;
 
   // thread tiles: the top level runs 2x4-position items (fused with a 4x8-pixel base
   // tile); deeper levels run one sub-band of a 4x4 or 2x4 tile per item

@@ -41,6 +41,7 @@ struct Plan2d {
   int tapset;            // floats per tap set
   // tiling
   int G;                 // channels per CTA
+  int g_shift;           // log2(G) when G is a power of two, else -1
   int TY, TX;            // output tile (multiples of 2^nlev unless a single tile)
   int ntile_y, ntile_x, ngroups;
   int nthreads;
@@ -63,7 +64,31 @@ struct Plan2d {
   int x_vec, y_vec;      // 16-byte channel chunks are legal for x / y
 };
 
-// Per-CTA geometry along one axis.
+// Geometry of one level along one axis for the tile [t0,t1), all in closed form so
+// that device code can evaluate just the levels it needs in registers:
+//   a    first position whose convolution output the tile needs   (t0 >> j)
+//   n    number of such positions
+//   lo   first position of the level that must hold data: the halo grows by a factor
+//        two per level going up, a - (K/2)*2^(d-j), clipped to the zero border
+//   hi   one past the last such position: (b_d + K/2) * 2^(d-j), clipped likewise
+//   org  position stored at array index 0: lo shifted left so that the first window
+//        (position a - K/2) starts on a multiple of (vmask+1) elements
+struct LevelGeo {
+  int a, n, lo, hi, org;
+};
+
+WT_HD LevelGeo level_geo(int d, int r, int rb, int j, int size_j, int t0, int t1, int vmask) {
+  LevelGeo g;
+  g.a = t0 >> j;
+  g.n = ((t1 + (1 << j) - 1) >> j) - g.a;
+  const int bd = (t1 + (1 << d) - 1) >> d;
+  g.lo = imax(g.a - (r << (d - j)), -rb);
+  g.hi = imin((bd + r) << (d - j), size_j + rb);
+  g.org = g.lo - ((g.lo - (g.a - r)) & vmask);
+  return g;
+}
+
+// Per-CTA geometry along one axis, all levels (host-side planning and the 1-D kernel).
 struct Axis {
   int t0, t1;                     // output range of the tile
   int a[kMaxFused + 1];           // first position whose convolution is needed at level j
@@ -77,40 +102,12 @@ struct Axis {
 // `vec_align` is 4 along x (window starts must be 16-byte aligned) and 1 along y.
 WT_HD void axis_geometry(int d, int r, int rb, int has_base, const int* size, int t0, int t1, int vec_align,
                          Axis& ax) {
+  (void)has_base;
   ax.t0 = t0;
   ax.t1 = t1;
-  ax.a[0] = t0;
-  ax.n[0] = t1 - t0;
-  int lo[kMaxFused + 1], hi[kMaxFused + 1];
-  for (int j = 1; j <= d; ++j) {
-    ax.a[j] = t0 >> j;
-    ax.n[j] = ((t1 + (1 << j) - 1) >> j) - ax.a[j];
-  }
-  for (int j = d; j >= 1; --j) {
-    lo[j] = ax.a[j] - r;
-    hi[j] = ax.a[j] + ax.n[j] + r;
-    if (j < d) {
-      lo[j] = imin(lo[j], 2 * lo[j + 1]);
-      hi[j] = imax(hi[j], 2 * hi[j + 1]);
-    }
-  }
-  if (d >= 1) {
-    lo[0] = 2 * lo[1];
-    hi[0] = 2 * hi[1];
-    if (has_base) {
-      lo[0] = imin(lo[0], t0 - r);
-      hi[0] = imax(hi[0], t1 + r);
-    }
-  } else {
-    lo[0] = t0 - r;
-    hi[0] = t1 + r;
-  }
   for (int j = 0; j <= d; ++j) {
-    ax.lo[j] = imax(lo[j], -rb);
-    ax.hi[j] = imin(hi[j], size[j] + rb);
-    // shift the origin left so that the first window (position a_j - r) lands on
-    // an index that is a multiple of vec_align
-    ax.org[j] = ax.lo[j] - pmod(ax.lo[j] - (ax.a[j] - r), vec_align);
+    const LevelGeo g = level_geo(d, r, rb, j, size[j], t0, t1, vec_align - 1);
+    ax.a[j] = g.a; ax.n[j] = g.n; ax.lo[j] = g.lo; ax.hi[j] = g.hi; ax.org[j] = g.org;
   }
 }
 

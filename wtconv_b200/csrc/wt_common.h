@@ -38,6 +38,12 @@ WT_HD int imin(int a, int b) { return a < b ? a : b; }
 WT_HD int imax(int a, int b) { return a > b ? a : b; }
 WT_HD int cdiv(int a, int b) { return (a + b - 1) / b; }
 WT_HD int round_up(int a, int b) { return cdiv(a, b) * b; }
+// log2 of the smallest power of two >= n, capped at 5 (one warp)
+WT_HD int lane_shift(int n) {
+  int s = 0;
+  while (s < 5 && (1 << s) < n) ++s;
+  return s;
+}
 // floor-mod for possibly negative a, positive b
 WT_HD int pmod(int a, int b) { int m = a % b; return m < 0 ? m + b : m; }
 
