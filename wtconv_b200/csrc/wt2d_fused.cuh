@@ -32,6 +32,9 @@
 
 #include "wt2d_plan.h"
 
+#ifndef WT_SKIP_MASK
+#define WT_SKIP_MASK 0
+#endif
 namespace wt {
 
 template <bool B, typename A, typename C> struct Select { typedef A type; };
@@ -312,11 +315,9 @@ WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, XT* __rest
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
-          if (ok) c[k].raw = *reinterpret_cast<const Raw*>(s0 + k * xs3);
-          else {
-#pragma unroll
-            for (int e = 0; e < V; ++e) c[k].set(e, Elem<T>::from_f(0.f));
-          }
+          Raw t = Raw();                         // zero bits = 0.0 in every activation type
+          if (ok) t = *reinterpret_cast<const Raw*>(s0 + k * xs3);
+          c[k].raw = t;
         }
         if constexpr (sizeof(XT) == 2) {
           // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
@@ -456,42 +457,32 @@ WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, int j, int oy, int 
     const int py = oy + rr;
     const int sy = 2 * py - soy;
     const bool rowok = py >= 0 && py < Hj && sy >= 0 && sy + 1 < srows;
-    const ST* s0 = src0 + g * splane + sy * sp;
+    // rows / columns whose source block is not on chip read a clamped (valid) address and
+    // are zeroed by a select, so that the loop has no divergent branch
+    const ST* s0 = src0 + g * splane + imin(imax(sy, 0), srows - 2) * sp;
     float* orow = sm.sub(j, g, 0) + rr * pitch;
     for (int gq = w.col0; gq < ngrp; gq += 32) {
       const int px0 = ox + 4 * gq;
       const int sx0 = 2 * px0 - sox;
       float o[4][4];
 #pragma unroll
-      for (int s = 0; s < 4; ++s)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) o[s][k] = 0.f;
-      if (rowok) {
-        float a[8], b[8];
-        const bool full = px0 >= 0 && px0 + 3 < Wj && sx0 >= 0 && sx0 + 7 < sp;
-        if (full && ((K / 2) % 2 == 0)) {          // even radius: source column pairs are aligned
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            load2(s0 + sx0 + 2 * k, a[2 * k], a[2 * k + 1]);
-            load2(s0 + sp + sx0 + 2 * k, b[2 * k], b[2 * k + 1]);
-          }
+      for (int k = 0; k < 4; ++k) {
+        const int px = px0 + k, sx = sx0 + 2 * k;
+        const bool ok = rowok && px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
+        const int cx = imin(imax(sx, 0), sp - 2);
+        float a0, a1, b0, b1;
+        if ((K / 2) % 2 == 0) {                    // even radius: source column pairs are aligned
+          load2(s0 + (cx & ~1), a0, a1);
+          load2(s0 + sp + (cx & ~1), b0, b1);
         } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int px = px0 + k, sx = sx0 + 2 * k;
-            const bool ok = px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
-            a[2 * k] = ok ? Elem<ST>::to_f(s0[sx]) : 0.f;
-            a[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sx + 1]) : 0.f;
-            b[2 * k] = ok ? Elem<ST>::to_f(s0[sp + sx]) : 0.f;
-            b[2 * k + 1] = ok ? Elem<ST>::to_f(s0[sp + sx + 1]) : 0.f;
-          }
+          a0 = Elem<ST>::to_f(s0[cx]); a1 = Elem<ST>::to_f(s0[cx + 1]);
+          b0 = Elem<ST>::to_f(s0[sp + cx]); b1 = Elem<ST>::to_f(s0[sp + cx + 1]);
         }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float ab = a[2 * k] + a[2 * k + 1], cd = b[2 * k] + b[2 * k + 1];
-          const float amb = a[2 * k] - a[2 * k + 1], cmd = b[2 * k] - b[2 * k + 1];
-          o[0][k] = ab + cd; o[1][k] = ab - cd; o[2][k] = amb + cmd; o[3][k] = amb - cmd;
-        }
+        const float ab = a0 + a1, cd = b0 + b1, amb = a0 - a1, cmd = b0 - b1;
+        o[0][k] = ok ? ab + cd : 0.f;
+        o[1][k] = ok ? ab - cd : 0.f;
+        o[2][k] = ok ? amb + cmd : 0.f;
+        o[3][k] = ok ? amb - cmd : 0.f;
       }
       float* od = orow + 4 * gq;
 #pragma unroll
@@ -658,6 +649,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       }
     }
     // input tile -> X0; everything the tile does not take from the plane is zero
+    if (WT_SKIP_MASK & 1) continue;
     const LevelGeo gy = tg.y(0), gx = tg.x(0);
     FillRange fr;
     fr.ylo = imax(gy.lo, 0); fr.yhi = imin(gy.hi, p.H);
@@ -692,6 +684,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
     WT_PHASE(nthr) {
+      if (WT_SKIP_MASK & 2) continue;
       const int oy = tg.y(j).org, ox = tg.x(j).org, soy = tg.y(j - 1).org, sox = tg.x(j - 1).org;
       if (j == 1) analysis_level<K, XT>(p, sm, 1, oy, ox, soy, sox, sm.x0<XT>(0), p.plane[0], gc, tid, nthr);
       else analysis_level<K, float>(p, sm, j, oy, ox, soy, sox, sm.sub(j - 1, 0, 0), p.plane[j - 1], gc, tid, nthr);
@@ -701,6 +694,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   // ---- phase 2: deep levels bottom-up: per-sub-band convolutions into Y, then the
   //      low-pass accumulation and synthesis butterfly into R_{j-1}
   for (int j = d; j >= 2; --j) {
+    if (WT_SKIP_MASK & 4) break;
     WT_PHASE(nthr) {
       const LevelGeo ly = tg.y(j), lx = tg.x(j);
       const int th = p.th[j];
@@ -759,6 +753,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
+    if (WT_SKIP_MASK & 8) continue;
     const LevelGeo y0 = tg.y(0), x0g = tg.x(0);
     if (d >= 1) {
       const LevelGeo y1 = tg.y(1), x1 = tg.x(1);
@@ -793,6 +788,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
 
   // ---- phase 4: write the tile
   WT_PHASE(nthr) {
+    if (WT_SKIP_MASK & 16) continue;
     const int hn = tg.ty1 - tg.ty0, wn = tg.tx1 - tg.tx0;
     if (!FINAL) {
       float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)tg.ty0 * p.W + tg.tx0;
