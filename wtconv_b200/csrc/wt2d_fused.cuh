@@ -35,6 +35,9 @@
 #ifndef WT_SKIP_MASK
 #define WT_SKIP_MASK 0
 #endif
+#ifndef WT_MARK
+#define WT_MARK(k)
+#endif
 namespace wt {
 
 template <bool B, typename A, typename C> struct Select { typedef A type; };
@@ -285,18 +288,80 @@ struct FillRange {   // valid source range in plane coordinates and the array or
   int ylo, yhi, xlo, xhi, orgy, orgx;
 };
 
-// Channels-last: one item = four pixels x CB bytes of consecutive channels.
-// EDGE > 1: every pixel is the sum of an EDGE x EDGE block of source pixels (the
-// low-pass input of a deep stage, wtconv2d.py:49-54, formed straight from x).
-template <typename T, typename XT, int CB, int EDGE>
+// Channels-last: one item = four pixels x CB bytes of consecutive channels.  All loads are
+// unconditional (clamped to a valid pixel) so that they issue back to back -- two rows, eight
+// loads per thread in flight -- and pixels the tile must not take from the plane are zeroed by
+// a select afterwards.
+template <typename T, typename XT, int CB>
 WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, XT* __restrict__ dst, const FillRange& fr,
                           int tid, int nthr) {
   constexpr int VEC = Chunk<T, CB>::VEC;
   if (VEC < 1) return;
   constexpr int V = VEC > 0 ? VEC : 1;
+  constexpr int U = 2;                            // rows in flight per thread
   typedef typename RawChunk<CB>::type Raw;
   const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
   const int nch = p.G / V;                        // power of two (G and V are)
+  const int nsh = lane_shift(nch);
+  const int ncols = (pitch >> 2) * nch;
+  const int xs2 = (int)p.xs[2], xs3 = (int)p.xs[3];
+  const RowWalk w(ncols, tid, nthr);
+  for (int rr0 = w.row0; rr0 < rows; rr0 += U * w.step) {
+    for (int ci = w.col0; ci < ncols; ci += 32) {
+      const int gq = ci >> nsh, ch = ci & (nch - 1);
+      const int px0 = fr.orgx + 4 * gq;
+      Chunk<T, CB> c[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int py = fr.orgy + rr0 + u * w.step;
+        const T* s0 = src + imin(imax(py, 0), p.Hsrc - 1) * xs2 + ch * V;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          c[u][k].raw = *reinterpret_cast<const Raw*>(s0 + imin(imax(px0 + k, 0), p.Wsrc - 1) * xs3);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int rr = rr0 + u * w.step;
+        if (rr >= rows) break;
+        const int py = fr.orgy + rr;
+        const bool rowok = py >= fr.ylo && py < fr.yhi;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
+          if (!ok) c[u][k].raw = Raw();           // zero bits = 0.0 in every activation type
+        }
+        XT* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
+        if constexpr (sizeof(XT) == 2) {
+          // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            Chunk<T, 8> q;
+            q.set(0, c[u][0].get(e)); q.set(1, c[u][1].get(e)); q.set(2, c[u][2].get(e)); q.set(3, c[u][3].get(e));
+            *reinterpret_cast<uint2*>(dd + e * plane) = q.raw;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            store4(dd + e * plane, Elem<T>::to_f(c[u][0].get(e)), Elem<T>::to_f(c[u][1].get(e)),
+                   Elem<T>::to_f(c[u][2].get(e)), Elem<T>::to_f(c[u][3].get(e)));
+        }
+      }
+    }
+  }
+}
+
+// Channels-last with reduction: every destination pixel is the sum of an EDGE x EDGE block of
+// source pixels (the low-pass input of a deep stage, wtconv2d.py:49-54, formed straight from x).
+// 4*EDGE*EDGE unconditional loads per item, then predicated accumulation.
+template <typename T, int CB, int EDGE>
+WT_HD void fill_x0_chunks_reduced(const Plan2d& p, const T* __restrict__ src, float* __restrict__ dst,
+                                  const FillRange& fr, int tid, int nthr) {
+  constexpr int VEC = Chunk<T, CB>::VEC;
+  if (VEC < 1) return;
+  constexpr int V = VEC > 0 ? VEC : 1;
+  typedef typename RawChunk<CB>::type Raw;
+  const int rows = p.rows[0], pitch = p.pitch[0], plane = p.plane[0];
+  const int nch = p.G / V;
   const int nsh = lane_shift(nch);
   const int ncols = (pitch >> 2) * nch;
   const int xs2 = (int)p.xs[2], xs3 = (int)p.xs[3];
@@ -307,64 +372,40 @@ WT_HD void fill_x0_chunks(const Plan2d& p, const T* __restrict__ src, XT* __rest
     for (int ci = w.col0; ci < ncols; ci += 32) {
       const int gq = ci >> nsh, ch = ci & (nch - 1);
       const int px0 = fr.orgx + 4 * gq;
-      XT* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
-      float v[4][V];
-      if (EDGE == 1) {
-        Chunk<T, CB> c[4];
-        const T* s0 = src + py * xs2 + px0 * xs3 + ch * V;
+      Chunk<T, CB> c[4][EDGE * EDGE];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const bool ok = rowok && (px0 + k) >= fr.xlo && (px0 + k) < fr.xhi;
-          Raw t = Raw();                         // zero bits = 0.0 in every activation type
-          if (ok) t = *reinterpret_cast<const Raw*>(s0 + k * xs3);
-          c[k].raw = t;
-        }
-        if constexpr (sizeof(XT) == 2) {
-          // X0 keeps the 16-bit activation type: a pure 4 x V transpose, no conversion
+      for (int k = 0; k < 4; ++k) {
+        const int px = imax(px0 + k, 0);
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            Chunk<T, 8> q;
-            q.set(0, c[0].get(e)); q.set(1, c[1].get(e)); q.set(2, c[2].get(e)); q.set(3, c[3].get(e));
-            *reinterpret_cast<uint2*>(dd + e * plane) = q.raw;
-          }
-          continue;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-#pragma unroll
-          for (int e = 0; e < V; ++e) v[k][e] = Elem<T>::to_f(c[k].get(e));
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-#pragma unroll
-          for (int e = 0; e < V; ++e) v[k][e] = 0.f;
-          const int px = px0 + k;
-          if (rowok && px >= fr.xlo && px < fr.xhi) {
-            Chunk<T, CB> c[EDGE * EDGE];
-            bool ok[EDGE * EDGE];
-            const T* s0 = src + (py * EDGE) * xs2 + (px * EDGE) * xs3 + ch * V;
-#pragma unroll
-            for (int b = 0; b < EDGE * EDGE; ++b) {
-              ok[b] = (py * EDGE + b / EDGE) < p.Hsrc && (px * EDGE + b % EDGE) < p.Wsrc;
-              if (ok[b]) c[b].raw = *reinterpret_cast<const Raw*>(s0 + (b / EDGE) * xs2 + (b % EDGE) * xs3);
-            }
-#pragma unroll
-            for (int by = 0; by < EDGE; ++by) {
-              float racc[V];
-#pragma unroll
-              for (int e = 0; e < V; ++e) racc[e] = 0.f;
-#pragma unroll
-              for (int bx = 0; bx < EDGE; ++bx)
-                if (ok[by * EDGE + bx]) {
-#pragma unroll
-                  for (int e = 0; e < V; ++e) racc[e] += Elem<T>::to_f(c[by * EDGE + bx].get(e));
-                }
-#pragma unroll
-              for (int e = 0; e < V; ++e) v[k][e] += racc[e];
-            }
-          }
+        for (int b = 0; b < EDGE * EDGE; ++b) {
+          const int sy = imin(imax(py, 0) * EDGE + b / EDGE, p.Hsrc - 1);
+          const int sx = imin(px * EDGE + b % EDGE, p.Wsrc - 1);
+          c[k][b].raw = *reinterpret_cast<const Raw*>(src + sy * xs2 + sx * xs3 + ch * V);
         }
       }
+      float v[4][V];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int px = px0 + k;
+        const bool pok = rowok && px >= fr.xlo && px < fr.xhi;
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[k][e] = 0.f;
+#pragma unroll
+        for (int by = 0; by < EDGE; ++by) {
+          float racc[V];
+#pragma unroll
+          for (int e = 0; e < V; ++e) racc[e] = 0.f;
+#pragma unroll
+          for (int bx = 0; bx < EDGE; ++bx) {
+            const bool ok = pok && (py * EDGE + by) < p.Hsrc && (px * EDGE + bx) < p.Wsrc;
+#pragma unroll
+            for (int e = 0; e < V; ++e) racc[e] += ok ? Elem<T>::to_f(c[k][by * EDGE + bx].get(e)) : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < V; ++e) v[k][e] += racc[e];
+        }
+      }
+      float* dd = dst + (ch * V) * plane + rr * pitch + 4 * gq;
 #pragma unroll
       for (int e = 0; e < V; ++e) store4(dd + e * plane, v[0][e], v[1][e], v[2][e], v[3][e]);
     }
@@ -580,15 +621,15 @@ WT_HD void move_plane_rows(float* __restrict__ gmem, int gplane, int gpitch, flo
       float* sp = smem_arr + g * splane + yy * spitch + 4 * gq;
       const bool whole = vec_ok && 4 * gq + 3 < nc;
       if (LOAD) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (whole) t = *reinterpret_cast<const float4*>(gp);
+        if (whole) async_copy16(sp, gp);
         else {
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
           if (4 * gq + 0 < nc) t.x = gp[0];
           if (4 * gq + 1 < nc) t.y = gp[1];
           if (4 * gq + 2 < nc) t.z = gp[2];
           if (4 * gq + 3 < nc) t.w = gp[3];
+          *reinterpret_cast<float4*>(sp) = t;
         }
-        *reinterpret_cast<float4*>(sp) = t;
       } else {
         const float4 t = *reinterpret_cast<const float4*>(sp);
         if (whole) *reinterpret_cast<float4*>(gp) = t;
@@ -634,6 +675,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   Smem2d sm{smem, &p};
   T* out_tile = reinterpret_cast<T*>(smem + p.ooff);
 
+  WT_MARK(0)
   // ---- phase 0: stage the tap sets this stage uses, the input tile and the deeper reconstruction
   WT_PHASE(nthr) {
     {
@@ -645,9 +687,20 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       for (int g = w.row0; g < gc; g += w.step) {
         const float4* src = reinterpret_cast<const float4*>(packed + (size_t)(c0 + g) * p.wstride);
         float4* dst = reinterpret_cast<float4*>(smem + p.woff + g * p.wsm);
-        for (int k = w.col0; k < per; k += 32) dst[k] = src[k < nbase ? k : k + skip];
+        for (int k = w.col0; k < per; k += 32) async_copy16(dst + k, src + (k < nbase ? k : k + skip));
       }
     }
+    // reconstruction of the deeper levels, produced by an earlier launch: asynchronous copies,
+    // in flight while the input tile is loaded below
+    if (p.has_rin) {
+      const LevelGeo dy = tg.y(d), dx = tg.x(d);
+      const int Hd = p.Hj[d], Wd = p.Wj[d];
+      float* rb = const_cast<float*>(rin) + ((size_t)nb * p.C + c0) * (size_t)(Hd * Wd) + (size_t)dy.a * Wd + dx.a;
+      const bool vec_ok = ((Wd & 3) == 0) && ((dx.a & 3) == 0) && (((Hd * Wd) & 3) == 0);
+      move_plane_rows<true>(rb, Hd * Wd, Wd, smem + p.roff[d], p.rplane[d], p.rpitch[d], gc, dy.n, dx.n, vec_ok,
+                            tid, nthr);
+    }
+    WT_MARK(6)
     // input tile -> X0; everything the tile does not take from the plane is zero
     if (WT_SKIP_MASK & 1) continue;
     const LevelGeo gy = tg.y(0), gx = tg.x(0);
@@ -657,30 +710,23 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     fr.orgy = gy.org; fr.orgx = gx.org;
     const T* xb = x + (size_t)nb * p.xs[0] + (size_t)c0 * p.xs[1];
     XT* x0arr = sm.x0<XT>(0);
-    if (p.x_vec && gc == p.G && p.in_shift <= 1) {
-      if (FINAL || p.in_shift == 0) {
-        if (p.x_vec == 16) fill_x0_chunks<T, XT, 16, 1>(p, xb, x0arr, fr, tid, nthr);
-        else if (p.x_vec == 8) fill_x0_chunks<T, XT, 8, 1>(p, xb, x0arr, fr, tid, nthr);
-        else fill_x0_chunks<T, XT, 4, 1>(p, xb, x0arr, fr, tid, nthr);
-      } else {
-        if (p.x_vec == 16) fill_x0_chunks<T, XT, 16, 2>(p, xb, x0arr, fr, tid, nthr);
-        else if (p.x_vec == 8) fill_x0_chunks<T, XT, 8, 2>(p, xb, x0arr, fr, tid, nthr);
-        else fill_x0_chunks<T, XT, 4, 2>(p, xb, x0arr, fr, tid, nthr);
-      }
+    if (p.x_vec && gc == p.G && p.in_shift == 0) {
+      if (p.x_vec == 16) fill_x0_chunks<T, XT, 16>(p, xb, x0arr, fr, tid, nthr);
+      else if (p.x_vec == 8) fill_x0_chunks<T, XT, 8>(p, xb, x0arr, fr, tid, nthr);
+      else fill_x0_chunks<T, XT, 4>(p, xb, x0arr, fr, tid, nthr);
+    } else if (!FINAL && p.x_vec && gc == p.G && p.in_shift == 1) {
+      float* xf = reinterpret_cast<float*>(x0arr);      // deep stages keep X0 in fp32
+      if (p.x_vec == 16) fill_x0_chunks_reduced<T, 16, 2>(p, xb, xf, fr, tid, nthr);
+      else if (p.x_vec == 8) fill_x0_chunks_reduced<T, 8, 2>(p, xb, xf, fr, tid, nthr);
+      else fill_x0_chunks_reduced<T, 4, 2>(p, xb, xf, fr, tid, nthr);
     } else {
       fill_x0_planar<T, XT>(p, xb, x0arr, fr, gc, tid, nthr);
     }
-    // reconstruction of the deeper levels, produced by an earlier launch
-    if (p.has_rin) {
-      const LevelGeo dy = tg.y(d), dx = tg.x(d);
-      const int Hd = p.Hj[d], Wd = p.Wj[d];
-      float* rb = const_cast<float*>(rin) + ((size_t)nb * p.C + c0) * (size_t)(Hd * Wd) + (size_t)dy.a * Wd + dx.a;
-      const bool vec_ok = ((Wd & 3) == 0) && ((dx.a & 3) == 0) && (((Hd * Wd) & 3) == 0);
-      move_plane_rows<true>(rb, Hd * Wd, Wd, smem + p.roff[d], p.rplane[d], p.rpitch[d], gc, dy.n, dx.n, vec_ok,
-                            tid, nthr);
-    }
+    WT_MARK(7)
+    async_wait_all();
   }
 
+  WT_MARK(1)
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
     WT_PHASE(nthr) {
@@ -691,6 +737,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
+  WT_MARK(2)
   // ---- phase 2: deep levels bottom-up: per-sub-band convolutions into Y, then the
   //      low-pass accumulation and synthesis butterfly into R_{j-1}
   for (int j = d; j >= 2; --j) {
@@ -750,6 +797,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
+  WT_MARK(3)
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
@@ -786,6 +834,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
+  WT_MARK(4)
   // ---- phase 4: write the tile
   WT_PHASE(nthr) {
     if (WT_SKIP_MASK & 16) continue;
@@ -811,6 +860,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       }
     }
   }
+  WT_MARK(5)
 }
 
 }  // namespace wt

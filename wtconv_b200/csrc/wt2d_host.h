@@ -136,7 +136,7 @@ inline long long layout_stage(Plan2d& p) {
     const int tile_y = imin(p.TY, p.H), tile_x = imin(p.TX, p.W);
     const int items = (d >= 1) ? p.G * cdiv((tile_y + 1) / 2, 2) * cdiv((tile_x + 1) / 2, 4)
                                : p.G * cdiv(tile_y, 4) * cdiv(tile_x, 8);
-    p.nthreads = imin(256, imax(64, round_up(items, 32)));
+    p.nthreads = imin(256, imax(128, round_up(items, 32)));
   }
   return off * 4;
 }

@@ -59,6 +59,23 @@ WT_HD int packed_channel_floats(int K, int ndim, int L) {
   return tapset_floats(K, ndim) * (1 + sub * L);
 }
 
+// 16-byte asynchronous copy global -> shared (cp.async, no register staging).  Both addresses
+// must be 16-byte aligned.  async_wait_all() makes the calling thread's copies visible to it;
+// the CTA barrier that ends the phase publishes them to the other threads.
+WT_HD void async_copy16(void* smem_dst, const void* gmem_src) {
+#ifdef __CUDA_ARCH__
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src) : "memory");
+#else
+  *static_cast<uint4*>(smem_dst) = *static_cast<const uint4*>(gmem_src);
+#endif
+}
+WT_HD void async_wait_all() {
+#ifdef __CUDA_ARCH__
+  asm volatile("cp.async.wait_all;" ::: "memory");
+#endif
+}
+
 template <typename T> struct Elem;
 template <> struct Elem<float> {
   static WT_HD float to_f(float v) { return v; }
