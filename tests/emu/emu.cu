@@ -52,11 +52,12 @@ void run2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* pa
 template <typename T, int K>
 void run1d(const Plan1d& p, const void* x, void* y, const float* packed) {
   AlignedBuf smem(p.smem_floats + 16);
-  const long long blocks = (long long)p.ntile * p.ngroups * p.B;
-  for (long long b = 0; b < blocks; ++b) {
-    for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
-    wt1d_cta<T, K>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, smem.p, (int)b);
-  }
+  for (int nb = 0; nb < p.B; ++nb)
+    for (int cg = 0; cg < p.ngroups; ++cg)
+      for (int tile = 0; tile < p.ntile; ++tile) {
+        for (int i = 0; i < p.smem_floats + 16; ++i) smem.p[i] = 1.0e30f;
+        wt1d_cta<T, K>(p, static_cast<const T*>(x), static_cast<T*>(y), packed, smem.p, tile, cg, nb);
+      }
 }
 
 template <int K>

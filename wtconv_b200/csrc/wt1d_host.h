@@ -7,7 +7,7 @@ namespace wt {
 
 constexpr int kThreads1d = 256;
 constexpr int kSmemLimit1d = 232448;
-constexpr int kSmemTwoPerSm1d = 113 * 1024;
+constexpr int kSmemTwoPerSm1d = 75 * 1024;   // three CTAs per SM
 
 struct Layer1d {
   int B, C, N, K, L, stride;
@@ -19,36 +19,49 @@ inline long long layout_1d(Plan1d& p) {
   p.r = p.K / 2;
   p.rb = imax(p.r, 1);
   p.tapset = tapset_floats(p.K, 1);
+  p.wsm = p.wstride;                          // all tap sets of a channel are staged
   p.nthreads = kThreads1d;
   p.Nj[0] = p.N;
   for (int j = 1; j <= d; ++j) p.Nj[j] = (p.Nj[j - 1] + 1) / 2;
   p.ntile = cdiv(p.N, p.TX);
   p.ngroups = cdiv(p.C, p.G);
+  p.g_shift = -1;
+  for (int k = 0; k < 8; ++k) if ((1 << k) == p.G) p.g_shift = k;
   int ext[kMaxFused + 1] = {0}, rext[kMaxFused + 1] = {0};
   for (int t = 0; t < p.ntile; ++t) {
     if (t >= 2 && t < p.ntile - 2) continue;   // interior tiles are all alike
     Axis ax;
     axis_geometry(d, p.r, p.rb, 1, p.Nj, t * p.TX, imin(p.N, (t + 1) * p.TX), 4, ax);
     for (int j = 0; j <= d; ++j) {
-      ext[j] = imax(ext[j], axis_extent(p.r, 1, ax, j, kTile1d));
-      rext[j] = imax(rext[j], round_up(ax.n[j], kTile1d));
+      // items cover 16 samples at level 0 and 8 positions at the levels above
+      ext[j] = imax(ext[j], axis_extent(p.r, 1, ax, j, j == 0 ? 2 * kTile1d : kTile1d));
+      rext[j] = imax(rext[j], round_up(ax.n[j], j == 0 ? 2 * kTile1d : kTile1d));
     }
   }
+  // row pitches padded so that consecutive channels start in different bank groups
+  const int lanes_g = imin(p.G, 8);
+  const int want = (lanes_g > 1) ? 4 * (8 / lanes_g) : 0;
+  auto pad = [&](int words) {
+    words = round_up(words, 4);
+    if (lanes_g > 1) while (words % 32 != want) words += 4;
+    return words;
+  };
   long long off = 0;
   p.woff = 0;
-  off += (long long)p.G * p.wstride;
+  off += (long long)p.G * p.wsm;
   for (int j = 0; j <= d; ++j) {
-    p.pitch[j] = round_up(ext[j] + 4, 4);     // +4: windows may over-read three floats
+    p.pitch[j] = pad(ext[j] + 4);             // +4: windows may over-read three floats
     p.off[j] = (int)off;
     off += (long long)p.G * (j == 0 ? 1 : 2) * p.pitch[j];
   }
   for (int j = 0; j <= d; ++j) {
-    const bool needed = (j < d) || (j == 0);
-    p.rpitch[j] = needed ? round_up(rext[j], 4) : 0;
+    // R_j feeds the level-j items; R_0 exists only when the output is pooled
+    const bool needed = (j == 0) ? (p.out_stride > 1) : (j < d);
+    p.rpitch[j] = needed ? pad(rext[j]) : 0;
     p.roff[j] = (int)off;
     off += (long long)p.G * p.rpitch[j];
   }
-  off = (off + 3) / 4 * 4;
+  off = (off + 3) / 4 * 4 + 4;
   p.smem_floats = (int)off;
   return off * 4;
 }
@@ -68,7 +81,7 @@ inline int plan_1d(Plan1d& p, long long& smem, const Layer1d& ly) {
   int TX;
   if (unit >= ly.N || unit > 8192) TX = ly.N;           // one tile spans the signal
   else {
-    long long t = (2048 / unit) * unit;
+    long long t = (1024 / unit) * unit;
     if (t == 0) t = unit;
     TX = (int)(t >= ly.N ? ly.N : t);
   }

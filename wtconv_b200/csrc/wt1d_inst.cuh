@@ -10,7 +10,7 @@ __global__ void __launch_bounds__(256, 2)
 wt1d_fused_kernel(const __grid_constant__ Plan1d p, const T* __restrict__ x, T* __restrict__ y,
                   const float* __restrict__ packed) {
   extern __shared__ __align__(16) float wt_smem[];
-  wt1d_cta<T, K>(p, x, y, packed, wt_smem, blockIdx.x);
+  wt1d_cta<T, K>(p, x, y, packed, wt_smem, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 template <typename T, int K>
@@ -19,8 +19,8 @@ static cudaError_t launch_one_1d(const Plan1d& p, const void* x, void* y, const 
   auto kern = wt1d_fused_kernel<T, K>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess) return e;
-  const long long blocks = (long long)p.ntile * p.ngroups * p.B;
-  kern<<<(unsigned)blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), static_cast<T*>(y), packed);
+  const dim3 blocks((unsigned)p.ntile, (unsigned)p.ngroups, (unsigned)p.B);
+  kern<<<blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), static_cast<T*>(y), packed);
   return cudaGetLastError();
 }
 

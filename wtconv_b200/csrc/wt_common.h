@@ -70,6 +70,16 @@ WT_HD void async_copy16(void* smem_dst, const void* gmem_src) {
   *static_cast<uint4*>(smem_dst) = *static_cast<const uint4*>(gmem_src);
 #endif
 }
+// 4-byte asynchronous copy; when `valid` is false nothing is read and zero is written
+WT_HD void async_copy4_zfill(void* smem_dst, const void* gmem_src, bool valid) {
+#ifdef __CUDA_ARCH__
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(gmem_src), "r"(n) : "memory");
+#else
+  *static_cast<unsigned int*>(smem_dst) = valid ? *static_cast<const unsigned int*>(gmem_src) : 0u;
+#endif
+}
 WT_HD void async_wait_all() {
 #ifdef __CUDA_ARCH__
   asm volatile("cp.async.wait_all;" ::: "memory");
