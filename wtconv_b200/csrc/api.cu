@@ -43,15 +43,15 @@ cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, cons
   }
 }
 
-// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group"
+// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group,threads"
 // (integers, 0 = automatic).  Read once; absent in normal use.
 const Tuning2d& env_tuning() {
   static const Tuning2d t = [] {
     Tuning2d v;
     if (const char* e = getenv("WTCONV_TUNE")) {
-      int a = 0, b = 0, c = 0, d = 0, g = 0;
-      sscanf(e, "%d,%d,%d,%d,%d", &a, &b, &c, &d, &g);
-      v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g;
+      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0;
+      sscanf(e, "%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t);
+      v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g; v.threads = t;
     }
     return v;
   }();
@@ -282,7 +282,10 @@ int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, 
   }
   Plan1d p;
   long long smem = 0;
-  const int ps = plan_1d(p, smem, ly);
+  // WTCONV_TUNE1D="tile,group": planner overrides for tuning sweeps
+  static const int tune_tx = [] { const char* e = getenv("WTCONV_TUNE1D"); int a = 0, b = 0; if (e) sscanf(e, "%d,%d", &a, &b); return a; }();
+  static const int tune_g = [] { const char* e = getenv("WTCONV_TUNE1D"); int a = 0, b = 0; if (e) sscanf(e, "%d,%d", &a, &b); return b; }();
+  const int ps = plan_1d(p, smem, ly, tune_tx, tune_g);
   if (ps) return ps;
   return (int)launch_wt1d(p, dtype, x, y, packed, (size_t)smem, static_cast<cudaStream_t>(stream));
 }

@@ -67,7 +67,7 @@ inline long long layout_1d(Plan1d& p) {
 }
 
 // Returns 0 or a negative status.
-inline int plan_1d(Plan1d& p, long long& smem, const Layer1d& ly) {
+inline int plan_1d(Plan1d& p, long long& smem, const Layer1d& ly, int force_tx = 0, int force_g = 0) {
   if (ly.L > kMaxFused) return -3;
   p = Plan1d();
   p.B = ly.B; p.C = ly.C; p.N = ly.N; p.K = ly.K; p.nlev = ly.L;
@@ -85,6 +85,7 @@ inline int plan_1d(Plan1d& p, long long& smem, const Layer1d& ly) {
     if (t == 0) t = unit;
     TX = (int)(t >= ly.N ? ly.N : t);
   }
+  if (force_tx > 0) TX = (int)imin((long long)ly.N, round_up(force_tx, (int)unit));
   p.TX = TX;
   static const int cand[4] = {8, 4, 2, 1};
   int best = 0;
@@ -102,8 +103,9 @@ inline int plan_1d(Plan1d& p, long long& smem, const Layer1d& ly) {
     if (layout_1d(p) > kSmemLimit1d) return -6;
     best = 1;
   }
-  p.G = best;
+  p.G = force_g > 0 ? force_g : best;
   smem = layout_1d(p);
+  if (smem > kSmemLimit1d) return -6;
   return 0;
 }
 

@@ -15,6 +15,9 @@ constexpr int kSmemTwoPerSm = 113 * 1024;  // budget that lets two CTAs share on
 constexpr int kThreads2d = 256;
 constexpr int kTiledLevels = 2;            // levels fused per stage when a plane has to be tiled
 
+// Tuning override of the threads per CTA (0 = automatic); process-wide, set by plan_layer.
+inline int& tuning_threads() { static int v = 0; return v; }
+
 // thread-tile height for `n` rows out of a menu (largest first): cheapest padded
 // row count, with a small penalty for short tiles (they reuse fewer loaded rows)
 inline int pick_tile(int n, const int* menu, int nmenu, double small_penalty) {
@@ -137,6 +140,7 @@ inline long long layout_stage(Plan2d& p) {
     const int items = (d >= 1) ? p.G * cdiv((tile_y + 1) / 2, 2) * cdiv((tile_x + 1) / 2, 4)
                                : p.G * cdiv(tile_y, 4) * cdiv(tile_x, 8);
     p.nthreads = imin(256, imax(128, round_up(items, 32)));
+    if (tuning_threads() > 0) p.nthreads = tuning_threads();
   }
   return off * 4;
 }
@@ -228,6 +232,7 @@ struct Tuning2d {
   int tile_x = 0;
   int tile_levels = 0;   // levels fused per tiled stage
   int group = 0;         // channels per CTA
+  int threads = 0;       // threads per CTA
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -265,6 +270,7 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
 // Builds the launch chain of one layer.
 inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) {
   Chain2d ch;
+  tuning_threads() = tune.threads;
   // level sizes of the whole pyramid
   std::vector<int> Hl(ly.L + 1), Wl(ly.L + 1);
   Hl[0] = ly.H; Wl[0] = ly.W;
