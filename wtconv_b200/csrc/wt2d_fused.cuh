@@ -165,31 +165,44 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, in
   constexpr int TH = 2, TW = 4;
   float acc[2 * TH][2 * TW];
   {
-    const int pitch = p.pitch[1];
-    float y[4][TH][TW];
+    // the 2x2 block of a position starts from the deeper reconstruction (it enters all four
+    // outputs with a plus sign, like the low-pass band)
 #pragma unroll
+    for (int i = 0; i < TH; ++i) {
+      float t[4] = {0.f, 0.f, 0.f, 0.f};
+      if (has_r) load4(sm.rec(1, g) + (iy * TH + i) * p.rpitch[1] + ix * TW, t);
+#pragma unroll
+      for (int q = 0; q < TW; ++q) {
+        acc[2 * i][2 * q] = t[q]; acc[2 * i][2 * q + 1] = t[q];
+        acc[2 * i + 1][2 * q] = t[q]; acc[2 * i + 1][2 * q + 1] = t[q];
+      }
+    }
+    // one pass per sub-band (kept as a loop: four times less code to fetch); the synthesis
+    // butterfly (wavelet.py:70-75) is applied as signed accumulation: LH flips the odd row,
+    // HL the odd column, HH both
+    const int pitch = p.pitch[1];
+    const int sstep = p.G * p.plane[1];
+    const float* sb = sm.sub(1, g, 0) + wy1 * pitch + wx1;
+    const float* tp = sm.taps(g, 1, 0);
+#pragma unroll 1
     for (int s = 0; s < 4; ++s) {
+      float y[TH][TW];
 #pragma unroll
       for (int i = 0; i < TH; ++i)
 #pragma unroll
-        for (int q = 0; q < TW; ++q) y[s][i][q] = 0.f;
-      conv_tile<K, TH, TW, float>(sm.sub(1, g, s) + wy1 * pitch + wx1, pitch, sm.taps(g, 1, s), y[s]);
+        for (int q = 0; q < TW; ++q) y[i][q] = 0.f;
+      conv_tile<K, TH, TW, float>(sb + s * sstep, pitch, tp + s * p.tapset, y);
+      const float fy = (s & 1) ? -1.f : 1.f, fx = (s & 2) ? -1.f : 1.f, fxy = fx * fy;
+#pragma unroll
+      for (int i = 0; i < TH; ++i)
+#pragma unroll
+        for (int q = 0; q < TW; ++q) {
+          acc[2 * i][2 * q] += y[i][q];
+          acc[2 * i][2 * q + 1] = fmaf(fx, y[i][q], acc[2 * i][2 * q + 1]);
+          acc[2 * i + 1][2 * q] = fmaf(fy, y[i][q], acc[2 * i + 1][2 * q]);
+          acc[2 * i + 1][2 * q + 1] = fmaf(fxy, y[i][q], acc[2 * i + 1][2 * q + 1]);
+        }
     }
-    if (has_r) {
-      const float* rj = sm.rec(1, g) + (iy * TH) * p.rpitch[1] + ix * TW;
-#pragma unroll
-      for (int i = 0; i < TH; ++i) {
-        float t[4];
-        load4(rj + i * p.rpitch[1], t);
-        y[0][i][0] += t[0]; y[0][i][1] += t[1]; y[0][i][2] += t[2]; y[0][i][3] += t[3];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < TH; ++i)
-#pragma unroll
-      for (int q = 0; q < TW; ++q)
-        synth4(y[0][i][q], y[1][i][q], y[2][i][q], y[3][i][q], acc[2 * i][2 * q], acc[2 * i][2 * q + 1],
-               acc[2 * i + 1][2 * q], acc[2 * i + 1][2 * q + 1]);
   }
   if (FUSE_BASE) {
     const int pitch = p.pitch[0];
