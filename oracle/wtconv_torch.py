@@ -75,7 +75,7 @@ def wtconv2d_forward(x: torch.Tensor, params: Dict[str, torch.Tensor], stride: i
     levels = _levels(params)
     if filters is None:
         ana, syn = haar_filters_2d(c, torch.float32)
-        ana, syn = ana.to(x.dtype), syn.to(x.dtype)
+        ana, syn = ana.to(x.device, x.dtype), syn.to(x.device, x.dtype)
     else:
         ana, syn = filters
     ksz = params["base_conv.weight"].shape[-1]
@@ -117,7 +117,7 @@ def wtconv1d_forward(x: torch.Tensor, params: Dict[str, torch.Tensor], stride: i
     levels = _levels(params)
     if filters is None:
         ana, syn = haar_filters_1d(c, torch.float32)
-        ana, syn = ana.to(x.dtype), syn.to(x.dtype)
+        ana, syn = ana.to(x.device, x.dtype), syn.to(x.device, x.dtype)
     else:
         ana, syn = filters
     ksz = params["base_conv.weight"].shape[-1]

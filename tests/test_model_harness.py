@@ -1,0 +1,68 @@
+"""WTConvNeXt-T harness: parameter-count pin (CPU) and model-level parity on the GPU between
+the harness built with the B200 layer and the same harness built with an oracle-backed layer."""
+import pytest
+import torch
+import torch.nn as nn
+
+
+def test_parameter_count_matches_reference_log():
+    import wtconv_b200
+    from wtconv_b200.wtconvnext_harness import WTConvNeXtTiny
+    m = WTConvNeXtTiny(wtconv_b200.WTConv2d)
+    assert sum(p.numel() for p in m.parameters()) == 30595624      # logs/val_tiny.out:4 of the reference
+    assert sum(isinstance(c, wtconv_b200.WTConv2d) for c in m.modules()) == 18
+
+
+class _OracleWTConv2d(nn.Module):
+    """Same parameters as the layer under test, forward through the CPU oracle's operator sequence
+    (runs on whatever device the tensors are on) -- test infrastructure only."""
+
+    def __init__(self, c_in, c_out, kernel_size=5, stride=1, bias=True, wt_levels=1):
+        super().__init__()
+        import wtconv_b200
+        self.inner = wtconv_b200.WTConv2d(c_in, c_out, kernel_size=kernel_size, stride=stride, bias=bias,
+                                          wt_levels=wt_levels)
+        self.stride = stride
+
+    def forward(self, x):
+        from oracle import wtconv_torch
+        params = {k: v for k, v in self.inner.state_dict().items() if "filter" not in k}
+        return wtconv_torch.wtconv2d_forward(x, params, stride=self.stride)
+
+
+@pytest.mark.gpu
+def test_model_logits_match_oracle_layers():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import wtconv_b200
+    from wtconv_b200.wtconvnext_harness import WTConvNeXtTiny
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    ours = WTConvNeXtTiny(wtconv_b200.WTConv2d)
+    with torch.no_grad():
+        for m in ours.modules():                       # make the layers matter: default layer scale is 1e-6
+            if hasattr(m, "gamma"):
+                m.gamma.fill_(0.5)
+    ref = WTConvNeXtTiny(_OracleWTConv2d)
+    sd = ours.state_dict()
+    ref.load_state_dict({k.replace("conv_dw.", "conv_dw.inner."): v for k, v in sd.items()})
+    ours, ref = ours.to(dev).eval(), ref.to(dev).eval()
+    x = torch.randn(2, 3, 224, 224, device=dev)
+    tf32 = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False            # the stem / downsampling convs stay true fp32
+    try:
+        with torch.no_grad():
+            a = ours(x.contiguous(memory_format=torch.channels_last))
+            b32 = ref(x)
+            b64 = ref.double()(x.double())
+    finally:
+        torch.backends.cudnn.allow_tf32 = tf32
+
+    def nerr(u, v):
+        return float((u.double() - v.double()).abs().max() / v.double().abs().max())
+
+    # 18 blocks of fp32 round-off compound through the LayerNorms, so the yardstick is the fp64
+    # evaluation of the same network: the B200 layers must sit as close to it as the fp32 oracle does.
+    e_ours, e_oracle = nerr(a, b64), nerr(b32, b64)
+    assert e_ours <= max(2.0 * e_oracle, 2e-5), f"vs fp64: ours {e_ours:.3e}, fp32 oracle {e_oracle:.3e}"
+    assert nerr(a, b32) <= 5e-4, f"logit mismatch {nerr(a, b32):.3e}"
