@@ -104,6 +104,16 @@ int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype
                              const long long* x_strides, const long long* y_strides, size_t* bytes);
 
 /*
+ * Number of kernel launches wtconv2d_forward enqueues for this problem and
+ * layout (the stages of the launch chain plus the low-pass reductions feeding
+ * them).  For accounting by benchmarks and profilers; the reference has no
+ * counterpart (its forward issues about 8*L+3 ATen kernels,
+ * wtconv/wtconv2d.py:46-85).
+ */
+int wtconv2d_launch_count(int B, int C, int H, int W, int K, int L, int stride, int dtype,
+                          const long long* x_strides, const long long* y_strides, int* launches);
+
+/*
  * WTConv2d forward: y = base_scale*(base_conv(x)) + inverse-wavelet cascade of
  * the scaled per-level sub-band depthwise convolutions, optionally subsampled
  * by `stride`.  Replaces the whole body of WTConv2d.forward

@@ -49,6 +49,31 @@ void run2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* pa
   else run2d<__half, K>(p, x, y, packed, rin, rout);
 }
 
+// register-resident small-plane kernel: one call per CTA of its grid
+template <typename T, int NLEV, bool BASE>
+void run_regplane_lev(const RegPlane& a, const void* x, void* y, float* rout, const float* packed) {
+  AlignedBuf smem(32 * a.wpad + 16);
+  for (int nb = 0; nb < a.nbatch; ++nb)
+    for (int cg = 0; cg < a.ngroups; ++cg) {
+      for (int i = 0; i < 32 * a.wpad + 16; ++i) smem.p[i] = 1.0e30f;
+      regplane_cta<T, 5, 7, 7, NLEV, BASE>(a, static_cast<const T*>(x), static_cast<T*>(y), rout, packed, smem.p, cg, nb);
+    }
+}
+
+template <typename T, bool BASE>
+void run_regplane_t(const RegPlane& a, const void* x, void* y, float* rout, const float* packed) {
+  if (a.nlev == 1) run_regplane_lev<T, 1, BASE>(a, x, y, rout, packed);
+  else if (a.nlev == 2) run_regplane_lev<T, 2, BASE>(a, x, y, rout, packed);
+  else run_regplane_lev<T, 3, BASE>(a, x, y, rout, packed);
+}
+
+void run_regplane(const RegPlane& a, int dtype, const void* x, void* y, float* rout, const float* packed) {
+  if (!a.has_base) run_regplane_t<float, false>(a, x, y, rout, packed);
+  else if (dtype == 0) run_regplane_t<float, true>(a, x, y, rout, packed);
+  else if (dtype == 1) run_regplane_t<__nv_bfloat16, true>(a, x, y, rout, packed);
+  else run_regplane_t<__half, true>(a, x, y, rout, packed);
+}
+
 template <typename T, int K>
 void run1d(const Plan1d& p, const void* x, void* y, const float* packed) {
   AlignedBuf smem(p.smem_floats + 16);
@@ -106,7 +131,9 @@ int emu_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_t
 // multi-stage path with this tile edge and `levels` levels per stage (exercises halos
 // and the stage chain on small planes); group > 0 forces the channels per CTA; mode 2 tiles
 // every stage, which makes chains of three and more stages with materialised low-pass planes.
-static int g_force_edge = 0, g_force_levels = 0, g_force_group = 0, g_force_mode = 1;
+static int g_force_edge = 0, g_force_levels = 0, g_force_group = 0, g_force_mode = 1, g_force_regplane = 0;
+// -1: plan without the register-resident small-plane kernel, 0: automatic
+int emu_regplane(int mode) { g_force_regplane = mode; return 0; }
 int emu_force(int edge, int levels, int group, int mode) {
   g_force_edge = edge; g_force_levels = levels; g_force_group = group; g_force_mode = mode ? mode : 1;
   return 0;
@@ -126,6 +153,7 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
   tune.tile_x = g_force_edge;
   tune.tile_levels = g_force_levels;
   tune.group = g_force_group;
+  tune.regplane = g_force_regplane;
   Chain2d ch = plan_layer(ly, tune);
   if (ch.status) return ch.status;
   std::vector<float> ws((size_t)ch.scratch_floats + 4, 1.0e30f);
@@ -134,18 +162,23 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
     float* out = ws.data() + rd.out_off;
     if (rd.in_off < 0) {
       for (long long i = 0; i < total; ++i) {
-        out[i] = dtype == 0 ? reduce_value<float>(static_cast<const float*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3])
+        out[rd.out_cl ? reduce_cl_index(i, C, rd.Hout, rd.Wout) : i] = dtype == 0 ? reduce_value<float>(static_cast<const float*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3])
                : dtype == 1 ? reduce_value<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3])
                             : reduce_value<__half>(static_cast<const __half*>(x), i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, xs[0], xs[1], xs[2], xs[3]);
       }
     } else {
       const float* in = ws.data() + rd.in_off;
       for (long long i = 0; i < total; ++i)
-        out[i] = reduce_value<float>(in, i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift,
+        out[rd.out_cl ? reduce_cl_index(i, C, rd.Hout, rd.Wout) : i] = reduce_value<float>(in, i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift,
                                      (long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1);
     }
   }
-  if (info) { info[0] = (int)ch.stages.size(); info[1] = (int)ch.reduces.size(); info[2] = ch.stages.back().plan.G; info[3] = (int)ch.stages.back().smem_bytes; }
+  if (info) {
+    info[0] = (int)ch.stages.size(); info[1] = (int)ch.reduces.size(); info[2] = ch.stages.back().plan.G;
+    info[3] = (int)ch.stages.back().smem_bytes;
+    info[4] = 0;
+    for (const Stage2d& sg : ch.stages) info[4] += sg.kind == 1;
+  }
   for (const Stage2d& sg : ch.stages) {
     const bool from_x = sg.xin_off < 0;
     const bool final_stage = sg.rout_off < 0;
@@ -153,6 +186,10 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
     const float* rin = sg.rin_off < 0 ? nullptr : ws.data() + sg.rin_off;
     float* rout = final_stage ? nullptr : ws.data() + sg.rout_off;
     const int dt = from_x ? dtype : 0;
+    if (sg.kind == 1) {
+      run_regplane(sg.reg, dt, xin, final_stage ? y : nullptr, rout, packed);
+      continue;
+    }
     switch (K) {
       case 1: run2d_k<1>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
       case 3: run2d_k<3>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;

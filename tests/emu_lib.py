@@ -44,7 +44,7 @@ def lib():
     global _lib
     if _lib is None:
         _lib = ctypes.CDLL(build())
-        for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force"):
+        for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force", "emu_regplane"):
             getattr(_lib, name).restype = ctypes.c_int
     return _lib
 
@@ -76,8 +76,10 @@ def pack(params, ndim, C, K, L, param_dtype=torch.float32, filter_dtype=None):
     return packed
 
 
-def forward2d(x, packed, K, L, stride=1, force=(0, 0, 0), channels_last_out=None):
-    """x: CPU tensor (B,C,H,W) in any strides; returns (y, info)."""
+def forward2d(x, packed, K, L, stride=1, force=(0, 0, 0), channels_last_out=None, regplane=0):
+    """x: CPU tensor (B,C,H,W) in any strides; returns (y, info).  info = [stages, reductions,
+    channel group and shared memory of the last stage, register-resident stages, ...];
+    regplane=-1 plans without the register-resident small-plane kernel."""
     B, C, H, W = x.shape
     Ho, Wo = -(-H // stride), -(-W // stride)
     cl = x.stride(1) == 1 and C > 1 if channels_last_out is None else channels_last_out
@@ -86,11 +88,13 @@ def forward2d(x, packed, K, L, stride=1, force=(0, 0, 0), channels_last_out=None
         y = y.contiguous(memory_format=torch.channels_last)
     xs = (ctypes.c_longlong * 4)(*x.stride())
     ys = (ctypes.c_longlong * 4)(*y.stride())
-    info = (ctypes.c_int * 4)()
+    info = (ctypes.c_int * 8)()
     lib().emu_force(*(tuple(force) + (0,) * (4 - len(force))))
+    lib().emu_regplane(regplane)
     st = lib().emu_wtconv2d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, H, W, K, L, stride, DTYPE_CODE[x.dtype],
                                     xs, ys, info)
     lib().emu_force(0, 0, 0, 0)
+    lib().emu_regplane(0)
     assert st == 0, f"emulation status {st}"
     return y, list(info)
 
@@ -100,7 +104,7 @@ def forward1d(x, packed, K, L, stride=1, force=(0, 0, 0)):
     y = torch.full((B, C, N // stride), float("nan"), dtype=x.dtype)
     xs = (ctypes.c_longlong * 3)(*x.stride())
     ys = (ctypes.c_longlong * 3)(*y.stride())
-    info = (ctypes.c_int * 4)()
+    info = (ctypes.c_int * 8)()
     lib().emu_force(*(tuple(force) + (0,) * (4 - len(force))))
     st = lib().emu_wtconv1d_forward(_ptr(x), _ptr(y), _ptr(packed), B, C, N, K, L, stride, DTYPE_CODE[x.dtype],
                                     xs, ys, info)

@@ -62,3 +62,27 @@ def test_emulated_1d_tiles(name, force):
     edge = max(force[0] // unit, 1) * unit
     err, tol, info = _run(name, "nchw", (edge, 0, force[2]))
     assert err <= tol, f"{name}: err {err:.3e} (tiles={info[0]})"
+
+
+# Register-resident small-plane kernel: whole 7x7 layers and the bottom of pyramids whose planes
+# reach 7x7 (channels-last tensors); odd channel and batch counts exercise the lane / warp masks.
+@pytest.mark.parametrize("B,C,H,W,L,dtype", [
+    (3, 40, 7, 7, 2, torch.float32), (5, 33, 7, 7, 1, torch.float32), (2, 64, 7, 7, 3, torch.float32),
+    (9, 8, 7, 7, 2, torch.bfloat16), (2, 16, 14, 14, 3, torch.float32), (2, 9, 13, 14, 3, torch.float32),
+    (1, 12, 28, 27, 4, torch.float32), (1, 8, 56, 56, 5, torch.float16), (1, 8, 55, 53, 4, torch.float32),
+])
+def test_emulated_register_resident_bottom(B, C, H, W, L, dtype):
+    from oracle import wtconv_torch
+    torch.manual_seed(B * 1000 + C * 10 + L)
+    params = wtconv_torch.random_params(C, 5, L, ndim=2, bias=True)
+    x = torch.randn(B, C, H, W).to(dtype).contiguous(memory_format=torch.channels_last)
+    ref = wtconv_torch.wtconv2d_forward(x.double(), {k: v.double() for k, v in params.items()}).numpy()
+    packed = emu_lib.pack(params, 2, C, 5, L)
+    y, info = emu_lib.forward2d(x, packed, 5, L)
+    assert info[4] == 1, f"the register-resident stage was not planned: {info}"
+    assert not torch.isnan(y.float()).any()
+    tol = TOL[str(dtype).split(".")[1]]
+    assert max_err(y.double().numpy(), ref) <= tol
+    y2, info2 = emu_lib.forward2d(x, packed, 5, L, regplane=-1)
+    assert info2[4] == 0
+    assert max_err(y2.double().numpy(), ref) <= tol

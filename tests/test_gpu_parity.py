@@ -149,6 +149,28 @@ def test_random_shapes_2d(case):
     assert max_err(out.float().cpu().numpy(), ref.numpy()) <= TOL[dtype]
 
 
+# Pyramids whose planes reach 7x7 take the register-resident kernel at the bottom (channels-last):
+# odd channel counts and batch sizes exercise its lane and warp masks, stride 2 its fallback.
+@pytest.mark.parametrize("B,C,H,W,L,stride,dtype", [
+    (5, 40, 7, 7, 2, 1, torch.float32), (131, 33, 7, 7, 1, 1, torch.float32), (2, 64, 7, 7, 3, 1, torch.bfloat16),
+    (3, 72, 14, 14, 3, 1, torch.float32), (2, 9, 13, 14, 3, 1, torch.float16), (3, 100, 28, 27, 4, 1, torch.float32),
+    (2, 24, 56, 56, 5, 1, torch.bfloat16), (4, 16, 7, 7, 2, 2, torch.float32), (2, 8, 55, 53, 4, 2, torch.float32),
+])
+def test_register_resident_bottom(B, C, H, W, L, stride, dtype):
+    dev = _cuda()
+    params = wtconv_torch.random_params(C, 5, L, bias=True, seed=B + C + H)
+    g = torch.Generator().manual_seed(C * 100 + W)
+    x = torch.randn(B, C, H, W, generator=g)
+    m = _module(2, C, 5, L, stride, True, params, dtype, dev)
+    xt = x.to(dev).to(dtype).contiguous(memory_format=torch.channels_last)
+    with torch.no_grad():
+        out = m(xt)
+    ref = _oracle(2, x, params, stride, dtype if dtype != torch.float32 else torch.float64).float()
+    assert tuple(out.shape) == tuple(ref.shape)
+    assert not torch.isnan(out.float()).any()
+    assert max_err(out.float().cpu().numpy(), ref.numpy()) <= TOL[dtype]
+
+
 @pytest.mark.parametrize("shape,L", [((1, 8, 200, 264), 5), ((2, 4, 131, 77), 4), ((1, 16, 96, 300), 6)])
 @pytest.mark.parametrize("layout", ["nchw", "cl"])
 def test_large_planes_use_the_tiled_chain(shape, L, layout):

@@ -2,7 +2,10 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
+#include <memory>
 #include <mutex>
+#include <vector>
 
 #include "../../include/wtconv_b200.h"
 #include "wt1d_host.h"
@@ -88,6 +91,31 @@ int make_layer2d(Layer2d& ly, const void* x, const void* y, int B, int C, int H,
   return WTCONV_OK;
 }
 
+// Launch chains are pure functions of the layer description; the last few are kept so that a
+// model that calls the same layers step after step does not re-plan them.
+std::shared_ptr<const Chain2d> cached_chain(const Layer2d& ly) {
+  struct Entry { Layer2d key; std::shared_ptr<const Chain2d> chain; };
+  static std::mutex mu;
+  static std::vector<Entry> entries;
+  static size_t next = 0;
+  constexpr size_t kCapacity = 64;
+  Layer2d key;
+  memset(&key, 0, sizeof(key));          // padding bytes take part in the comparison
+  key.B = ly.B; key.C = ly.C; key.H = ly.H; key.W = ly.W; key.K = ly.K; key.L = ly.L; key.stride = ly.stride;
+  key.elem_size = ly.elem_size; key.x_align = ly.x_align; key.y_align = ly.y_align;
+  for (int i = 0; i < 4; ++i) { key.xs[i] = ly.xs[i]; key.ys[i] = ly.ys[i]; }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& e : entries)
+      if (memcmp(&e.key, &key, sizeof(key)) == 0) return e.chain;
+  }
+  auto chain = std::make_shared<const Chain2d>(plan_layer(ly, env_tuning()));
+  std::lock_guard<std::mutex> lock(mu);
+  if (entries.size() < kCapacity) entries.push_back({key, chain});
+  else { entries[next] = {key, chain}; next = (next + 1) % kCapacity; }
+  return chain;
+}
+
 }  // namespace
 
 extern "C" {
@@ -162,9 +190,22 @@ int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype
   // stride or on pointer alignment
   const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, x_strides, y_strides);
   if (st) return st;
-  const Chain2d ch = plan_layer(ly, env_tuning());
+  const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
+  const Chain2d& ch = *chp;
   if (ch.status) return ch.status;
   *bytes = (size_t)ch.scratch_floats * sizeof(float);
+  return WTCONV_OK;
+}
+
+int wtconv2d_launch_count(int B, int C, int H, int W, int K, int L, int stride, int dtype,
+                          const long long* x_strides, const long long* y_strides, int* launches) {
+  if (!launches) return WTCONV_ERR_BAD_ARG;
+  Layer2d ly;
+  const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, stride, dtype, x_strides, y_strides);
+  if (st) return st;
+  const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
+  if (chp->status) return chp->status;
+  *launches = (int)(chp->reduces.size() + chp->stages.size());
   return WTCONV_OK;
 }
 
@@ -176,7 +217,8 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
   const int st = make_layer2d(ly, x, y, B, C, H, W, K, L, stride, dtype, x_strides, y_strides);
   if (st) return st;
   if (ly.x_align < ly.elem_size || ly.y_align < ly.elem_size || ptr_align(packed) < 16) return WTCONV_ERR_MISALIGNED;
-  const Chain2d ch = plan_layer(ly, env_tuning());
+  const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
+  const Chain2d& ch = *chp;
   if (ch.status) return ch.status;
   float* ws = static_cast<float*>(workspace);
   if (ch.scratch_floats > 0) {
@@ -187,11 +229,11 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
   for (const Reduce2d& rd : ch.reduces) {
     cudaError_t e;
     if (rd.in_off < 0) {
-      e = launch_reduce(dtype, x, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, ly.xs, cs);
+      e = launch_reduce(dtype, x, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, ly.xs, rd.out_cl, cs);
     } else {
       const long long s[4] = {(long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1};
       e = launch_reduce(WTCONV_F32, ws + rd.in_off, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout,
-                        rd.shift, s, cs);
+                        rd.shift, s, rd.out_cl, cs);
     }
     if (e != cudaSuccess) return (int)e;
   }
@@ -201,8 +243,16 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     const void* xin = from_x ? x : static_cast<const void*>(ws + sg.xin_off);
     const float* rin = sg.rin_off < 0 ? nullptr : ws + sg.rin_off;
     float* rout = final_stage ? nullptr : ws + sg.rout_off;
-    const cudaError_t e = launch_wt2d(sg.plan, from_x ? dtype : WTCONV_F32, xin, final_stage ? y : nullptr, packed,
-                                      rin, rout, (size_t)sg.smem_bytes, cs);
+    const int in_dtype = from_x ? dtype : WTCONV_F32;
+    cudaError_t e;
+    switch (sg.kind) {
+      case 1:
+        e = launch_regplane(sg.reg, in_dtype, xin, final_stage ? y : nullptr, rout, packed, (size_t)sg.smem_bytes, cs);
+        break;
+      default:
+        e = launch_wt2d(sg.plan, in_dtype, xin, final_stage ? y : nullptr, packed, rin, rout, (size_t)sg.smem_bytes, cs);
+        break;
+    }
     if (e != cudaSuccess) return (int)e;
   }
   return WTCONV_OK;
@@ -219,7 +269,6 @@ namespace {
 // their 128-bit accesses are aligned whatever the offsets inside it.
 static __device__ __align__(256) unsigned char g_static_scratch[WTCONV_STATIC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_scratch_mutex;
 void* g_scratch_addr[kMaxDevices] = {nullptr};   // device address of g_static_scratch, per device
 

@@ -17,7 +17,8 @@ template <typename T, int K>
 static cudaError_t launch_one_1d(const Plan1d& p, const void* x, void* y, const float* packed,
                                  size_t smem_bytes, cudaStream_t stream) {
   auto kern = wt1d_fused_kernel<T, K>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  static bool done[kMaxDevices] = {false};
+  cudaError_t e = allow_full_smem(kern, done);
   if (e != cudaSuccess) return e;
   const dim3 blocks((unsigned)p.ntile, (unsigned)p.ngroups, (unsigned)p.B);
   kern<<<blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), static_cast<T*>(y), packed);

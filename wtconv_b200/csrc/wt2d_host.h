@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "wt2d_plan.h"
+#include "wt2d_regplane.cuh"
 
 namespace wt {
 
@@ -145,8 +146,43 @@ inline long long layout_stage(Plan2d& p) {
   return off * 4;
 }
 
+// Combinations of the register-resident small-plane kernel that are compiled in
+inline bool regplane_supported(int K, int PH, int PW, int nlev) {
+  return K == 5 && PH == 7 && PW == 7 && nlev >= 1 && nlev <= 3;
+}
+
+// Launch description of a register-resident stage: levels q+1 .. q+nlev on the PH x PW plane of
+// level q.  q = 0: the layer itself (tensor strides xs / ys, base path included); q > 0: the
+// plane set is the fp32 block-sum reduction of the layer input, (B,C,PH,PW)-contiguous.
+inline long long plan_regplane(RegPlane& a, int B, int C, int K, int L, int q, int nlev, int PH, int PW,
+                               const long long* xs, const long long* ys, bool reduced_cl) {
+  a = RegPlane();
+  a.B = B; a.C = C; a.PH = PH; a.PW = PW;
+  a.K = K; a.nlev = nlev; a.lvl0 = q; a.has_base = (q == 0) ? 1 : 0;
+  a.wstride = packed_channel_floats(K, 2, L);
+  const int ts = tapset_floats(K, 2);
+  a.wbeg = a.has_base ? 0 : ts * (1 + 4 * q);
+  a.wlen = ts * (a.has_base + 4 * nlev);
+  a.wpad = a.wlen + (((a.wlen / 4) % 2 == 0) ? 4 : 0);
+  a.ngroups = cdiv(C, 32);
+  // about one wave of CTAs (three per SM), so the tap sets are staged once per resident CTA
+  const long long warp_tasks = (long long)B * a.ngroups;
+  a.samples_per_warp = (int)imax(1, (int)((warp_tasks + kRegPlaneWarps * 444 - 1) / (kRegPlaneWarps * 444)));
+  a.nbatch = cdiv(B, kRegPlaneWarps * a.samples_per_warp);
+  const long long planar[4] = {(long long)C * PH * PW, (long long)PH * PW, PW, 1};
+  const long long chlast[4] = {(long long)C * PH * PW, 1, (long long)PW * C, C};
+  for (int i = 0; i < 4; ++i) {
+    a.xs[i] = (q == 0) ? xs[i] : (reduced_cl ? chlast[i] : planar[i]);
+    a.ys[i] = (q == 0) ? ys[i] : 0;
+    a.os[i] = planar[i];
+  }
+  return (long long)32 * a.wpad * 4;
+}
+
 struct Stage2d {
-  Plan2d plan;
+  int kind = 0;        // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg)
+  RegPlane reg;
+  Plan2d plan = Plan2d();
   long long xin_off;   // fp32 low-pass planes read as input (floats into scratch), -1: the layer input
   long long rin_off;   // reconstruction of the deeper levels read, -1: none
   long long rout_off;  // fp32 planes written, -1: the layer output
@@ -158,6 +194,7 @@ struct Reduce2d {
   long long in_off;    // -1: the layer input
   long long out_off;
   int Hin, Win, Hout, Wout, shift;
+  int out_cl = 0;      // 1: the sums are stored channel-fastest, (B,Hout,Wout,C), for the register-resident stage
 };
 
 struct Chain2d {
@@ -233,18 +270,20 @@ struct Tuning2d {
   int tile_levels = 0;   // levels fused per tiled stage
   int group = 0;         // channels per CTA
   int threads = 0;       // threads per CTA
+  int regplane = 0;      // -1: never use the register-resident small-plane kernel
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
 // group that lets two CTAs share an SM (or the forced one).  `good` tells whether that
 // group still moves at least 8 bytes per pixel of a channels-last tensor.
 inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer2d& ly, int H, int W,
-                             int first_level, int nlev, bool final_stage, int in_shift, int forced_group = 0) {
+                             int first_level, int nlev, bool final_stage, int in_shift, int forced_group = 0,
+                             bool has_rin = false) {
   good = false;
   if (nlev > kMaxFused) return false;
   const int TY = imax(H, 1), TX = imax(W, 1);
   if (forced_group > 0) {
-    smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, forced_group, TY, TX, in_shift);
+    smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, has_rin, forced_group, TY, TX, in_shift);
     good = smem <= kSmemLimitBytes;
     return good;
   }
@@ -254,13 +293,13 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
     const int G = cand[i];
     if (G > ly.C && G != 1) continue;
     Plan2d q;
-    const long long bytes = plan_stage(q, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX, in_shift);
+    const long long bytes = plan_stage(q, ly, H, W, first_level, nlev, final_stage, has_rin, G, TY, TX, in_shift);
     if (!fit_two && bytes <= kSmemTwoPerSm) fit_two = G;
     if (!fit_one && bytes <= kSmemLimitBytes) fit_one = G;
   }
   const int G = fit_two ? fit_two : fit_one;
   if (G == 0) return false;
-  smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, false, G, TY, TX, in_shift);
+  smem = plan_stage(p, ly, H, W, first_level, nlev, final_stage, has_rin, G, TY, TX, in_shift);
   const bool from_x = (first_level == 0) || in_shift > 0;
   const bool channels_last = from_x && ly.xs[1] == 1 && ly.C > 1;
   good = fit_two > 0 && (!channels_last || G * ly.elem_size >= 8 || G >= ly.C);
@@ -276,17 +315,41 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   Hl[0] = ly.H; Wl[0] = ly.W;
   for (int j = 1; j <= ly.L; ++j) { Hl[j] = (Hl[j - 1] + 1) / 2; Wl[j] = (Wl[j - 1] + 1) / 2; }
 
+  // Bottom of the pyramid: when the plane of some level q is small enough for the
+  // register-resident kernel (channels-last tensors, every remaining level), that kernel
+  // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
+  int qreg = -1;
+  const bool untuned = !tune.force_tiled && !tune.tile_y && !tune.tile_x && !tune.tile_levels && !tune.group;
+  if (untuned && tune.regplane >= 0 && ly.xs[1] == 1 && ly.C > 1) {
+    for (int q = 0; q < ly.L; ++q) {
+      if (!regplane_supported(ly.K, Hl[q], Wl[q], ly.L - q)) continue;
+      if (q == 0 && (ly.stride != 1 || ly.ys[1] != 1)) continue;
+      qreg = q;
+      break;
+    }
+  }
+  if (qreg == 0) {
+    Stage2d st;
+    st.kind = 1;
+    st.smem_bytes = plan_regplane(st.reg, ly.B, ly.C, ly.K, ly.L, 0, ly.L, Hl[0], Wl[0], ly.xs, ly.ys, false);
+    st.xin_off = -1; st.rin_off = -1; st.rout_off = -1;
+    ch.stages.push_back(st);
+    return ch;
+  }
+  const int Ltop = qreg > 0 ? qreg : ly.L;     // levels handled by CTA-tile stages
+  const bool below = qreg > 0;                 // their deepest stage reads a reconstruction from below
+
   // top-down: decide the stage boundaries.  A stage is "whole" (its plane and every
   // deeper level stay on chip) or "tiled" (a few levels on halo tiles, the rest below).
   struct Cut { int first, nlev; bool whole; };
   std::vector<Cut> cuts;
   int q = 0;
   while (true) {
-    const int remaining = ly.L - q;
+    const int remaining = Ltop - q;
     Plan2d tmp; long long bytes = 0; bool good = false;
     const bool fits = !(tune.force_tiled == 2 && remaining > 0) && !(tune.force_tiled && q == 0) &&
                       remaining <= kMaxFused &&
-                      plan_whole_plane(tmp, bytes, good, ly, Hl[q], Wl[q], q, remaining, q == 0, 0, tune.group);
+                      plan_whole_plane(tmp, bytes, good, ly, Hl[q], Wl[q], q, remaining, q == 0, 0, tune.group, below);
     // a deep stage (q > 0) that fits is always taken; the top stage only if it is efficient
     if (fits && (good || q > 0 || remaining == 0)) {
       cuts.push_back({q, remaining, true});
@@ -301,17 +364,24 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     }
     cuts.push_back({q, nlev, false});
     q += nlev;
-    if (q == ly.L) break;   // also ends a base-only layer (nlev == 0)
+    if (q == Ltop) break;   // also ends a base-only layer (nlev == 0)
   }
-  // With exactly one deep stage it reads the layer input itself and forms its low-pass
-  // plane while loading; with more, the low-pass planes are materialised in scratch.
+  // With exactly one deep CTA-tile stage it reads the layer input itself and forms its low-pass
+  // plane while loading; with more, the low-pass planes are materialised in scratch (as is
+  // the input of the register-resident stage).
   const bool direct = (cuts.size() == 2);
   long long off = 0;
-  std::vector<long long> xoff(cuts.size(), -1), roff(cuts.size(), -1);
+  std::vector<long long> xoff(cuts.size(), -1), roff(cuts.size() + 1, -1);
   for (size_t i = 1; i < cuts.size(); ++i) {
     const long long n = (long long)ly.B * ly.C * Hl[cuts[i].first] * Wl[cuts[i].first];
     if (!direct) { xoff[i] = off; off += (n + 3) / 4 * 4; }
     roff[i] = off; off += (n + 3) / 4 * 4;
+  }
+  long long reg_xoff = -1;
+  if (below) {
+    const long long n = (long long)ly.B * ly.C * Hl[qreg] * Wl[qreg];
+    reg_xoff = off; off += (n + 3) / 4 * 4;
+    roff[cuts.size()] = off; off += (n + 3) / 4 * 4;
   }
   ch.scratch_floats = off;
   if (!direct) {
@@ -325,17 +395,32 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
       ch.reduces.push_back(rd);
     }
   }
+  if (below) {
+    Reduce2d rd;                      // low-pass plane of level qreg straight from the layer input
+    rd.in_off = -1;
+    rd.out_off = reg_xoff;
+    rd.Hin = ly.H; rd.Win = ly.W; rd.Hout = Hl[qreg]; rd.Wout = Wl[qreg];
+    rd.shift = qreg;
+    rd.out_cl = 1;
+    ch.reduces.push_back(rd);
+    Stage2d st;
+    st.kind = 1;
+    st.smem_bytes = plan_regplane(st.reg, ly.B, ly.C, ly.K, ly.L, qreg, ly.L - qreg, Hl[qreg], Wl[qreg],
+                                  nullptr, nullptr, true);
+    st.xin_off = reg_xoff; st.rin_off = -1; st.rout_off = roff[cuts.size()];
+    ch.stages.push_back(st);
+  }
   for (int i = (int)cuts.size() - 1; i >= 0; --i) {
     Stage2d st;
     const Cut& c = cuts[i];
     const bool final_stage = (c.first == 0);
-    const bool has_rin = (i + 1 < (int)cuts.size());
+    const bool has_rin = (i + 1 < (int)cuts.size()) || below;
     const int in_shift = (direct && i == 1) ? c.first : 0;
     const int H = Hl[c.first], W = Wl[c.first];
     if (c.whole) {
       bool good = false;
       if (!plan_whole_plane(st.plan, st.smem_bytes, good, ly, H, W, c.first, c.nlev, final_stage, in_shift,
-                            final_stage ? tune.group : 0)) {
+                            final_stage ? tune.group : 0, has_rin)) {
         ch.status = -6; return ch;
       }
     } else {

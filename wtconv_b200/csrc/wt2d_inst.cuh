@@ -35,13 +35,15 @@ static cudaError_t launch_one(const Plan2d& p, const void* x, void* y, const flo
   const dim3 blocks((unsigned)p.ngroups, (unsigned)(p.ntile_x * p.ntile_y), (unsigned)p.B);
   if (p.has_base) {
     auto kern = wt2d_final_kernel<T, K>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    static bool done[kMaxDevices] = {false};
+    cudaError_t e = allow_full_smem(kern, done);
     if (e != cudaSuccess) return e;
     kern<<<blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), static_cast<T*>(y),
                                                                packed, rin);
   } else {
     auto kern = wt2d_deep_kernel<T, K>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    static bool done[kMaxDevices] = {false};
+    cudaError_t e = allow_full_smem(kern, done);
     if (e != cudaSuccess) return e;
     kern<<<blocks, p.nthreads, smem_bytes, stream>>>(p, static_cast<const T*>(x), packed, rin, rout);
   }

@@ -11,6 +11,7 @@ namespace wt {
 
 struct Plan2d;
 struct Plan1d;
+struct RegPlane;
 
 struct PackArgs {
   int C, L, taps, tapset, subbands;
@@ -81,12 +82,27 @@ WT_HD float reduce_value(const T* __restrict__ in, long long i, int C, int Hin, 
 
 cudaError_t launch_pack(const PackArgs& a, int param_dtype, float* packed, cudaStream_t stream);
 
+// out_cl: store the sums channel-fastest, (B,Hout,Wout,C), instead of as (B,C,Hout,Wout) planes
 cudaError_t launch_reduce(int dtype, const void* in, float* out, int B, int C, int Hin, int Win, int Hout,
-                          int Wout, int shift, const long long* strides, cudaStream_t stream);
+                          int Wout, int shift, const long long* strides, int out_cl, cudaStream_t stream);
+
+// index of element (n,c,yo,xo) of the plane-major index i in the channel-fastest output
+WT_HD long long reduce_cl_index(long long i, int C, int Hout, int Wout) {
+  const int xo = (int)(i % Wout);
+  long long t = i / Wout;
+  const int yo = (int)(t % Hout);
+  t /= Hout;
+  const int c = (int)(t % C);
+  const long long n = t / C;
+  return ((n * Hout + yo) * Wout + xo) * C + c;
+}
 
 template <int K>
 cudaError_t launch_wt2d_k(const Plan2d& p, int dtype, const void* x, void* y, const float* packed,
                           const float* rin, float* rout, size_t smem_bytes, cudaStream_t stream);
+
+cudaError_t launch_regplane(const RegPlane& a, int dtype, const void* x, void* y, float* rout,
+                            const float* packed, size_t smem_bytes, cudaStream_t stream);
 
 template <int K>
 cudaError_t launch_wt1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* packed,

@@ -86,6 +86,24 @@ WT_HD void async_wait_all() {
 #endif
 }
 
+#if defined(__CUDACC__)
+// Opt the kernel into the full dynamic shared memory of the SM once per device instead of on
+// every launch (a driver call each time).  `done` is a per-kernel table owned by the caller.
+constexpr int kMaxDevices = 64;
+constexpr int kMaxDynamicSmem = 232448;   // 227 KB
+template <typename Kern>
+inline cudaError_t allow_full_smem(Kern kern, bool (&done)[kMaxDevices]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+  if (e == cudaSuccess) done[dev] = true;
+  return e;
+}
+#endif
+
 template <typename T> struct Elem;
 template <> struct Elem<float> {
   static WT_HD float to_f(float v) { return v; }

@@ -22,6 +22,7 @@ from . import _lib
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 _SQRT_HALF = 1.0 / math.sqrt(2.0)
+_EMPTY = object()   # call record of an input without elements
 # db1 taps as PyWavelets tabulates them; the reference reads them through
 # pywt.Wavelet (wtconv/util/wavelet.py:7,24) and supports nothing the table lacks.
 _DB1 = dict(dec_lo=[_SQRT_HALF, _SQRT_HALF], dec_hi=[-_SQRT_HALF, _SQRT_HALF],
@@ -103,7 +104,7 @@ class _WTConvNd(nn.Module):
 
         self._packed = None
         self._packed_key = None
-        self._ws_cache = {}
+        self._call_cache = {}
 
     # -- parameter folding -------------------------------------------------
     def _kernel_params(self):
@@ -116,8 +117,8 @@ class _WTConvNd(nn.Module):
         """fp32 block of folded parameters, rebuilt only when a parameter changed
         (data pointer, in-place version counter, dtype or device)."""
         ps = self._kernel_params()
-        key = tuple((p.data_ptr(), p._version, p.dtype, p.device) if p is not None else None for p in ps) \
-            + (self.wt_filter.dtype,)
+        key = tuple((p.data_ptr(), p._version) if p is not None else None for p in ps) \
+            + (ps[0].dtype, ps[0].device, self.wt_filter.dtype)
         if self._packed is not None and key == self._packed_key and self._packed.device == device:
             return self._packed
         lib = _lib.load()
@@ -169,34 +170,57 @@ class WTConv2d(_WTConvNd):
     def forward(self, x):
         self._check_input(x)
         lib = _lib.load()
+        dev = x.device
+        # everything that depends only on the geometry of the call is computed once per
+        # (shape, strides, dtype): output layout, ctypes stride arrays, scratch size
+        key = (tuple(x.shape), x.stride(), x.dtype)
+        rec = self._call_cache.get(key)
+        if rec is None:
+            rec = self._call_cache[key] = self._plan_call(lib, x)
+        if rec is _EMPTY:
+            B, C, H, W = x.shape
+            s = self.stride
+            return x.new_empty((B, C, -(-H // s), -(-W // s)))
+        make_contiguous, out_shape, out_format, xs, ys, nbytes, dims = rec
+        if make_contiguous:
+            x = x.contiguous()
+        y = torch.empty(out_shape, dtype=x.dtype, device=dev, memory_format=out_format)
+        packed = self._packed_params(dev)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+        if torch.cuda.current_device() == dev.index:
+            st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
+                                      ws.data_ptr() if ws is not None else None, nbytes, *dims, xs, ys,
+                                      torch.cuda.current_stream(dev).cuda_stream)
+        else:
+            with torch.cuda.device(dev):
+                st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
+                                          ws.data_ptr() if ws is not None else None, nbytes, *dims, xs, ys,
+                                          torch.cuda.current_stream(dev).cuda_stream)
+        if st:
+            _lib.check(st, "wtconv2d_forward")
+        return y
+
+    def _plan_call(self, lib, x):
         B, C, H, W = x.shape
         s = self.stride
         if x.numel() == 0:
-            return x.new_empty((B, C, -(-H // s), -(-W // s)))
+            return _EMPTY
         channels_last = x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()
-        if not channels_last and not x.is_contiguous():
+        make_contiguous = not channels_last and not x.is_contiguous()
+        if make_contiguous:
             x = x.contiguous()
-        y = torch.empty((B, C, -(-H // s), -(-W // s)), dtype=x.dtype, device=x.device,
-                        memory_format=torch.channels_last if channels_last else torch.contiguous_format)
-        packed = self._packed_params(x.device)
+        out_shape = (B, C, -(-H // s), -(-W // s))
+        out_format = torch.channels_last if channels_last else torch.contiguous_format
+        y = torch.empty(out_shape, dtype=x.dtype, device="meta", memory_format=out_format)
         K, L, code = self.kernel_size, self.wt_levels, _DTYPE_CODE[x.dtype]
         xs = (ctypes.c_longlong * 4)(*x.stride())
         ys = (ctypes.c_longlong * 4)(*y.stride())
-        key = (B, C, H, W, code, channels_last)
-        nbytes = self._ws_cache.get(key)
-        if nbytes is None:
-            out = ctypes.c_size_t(0)
-            _lib.check(lib.wtconv2d_workspace_bytes(B, C, H, W, K, L, code, xs, ys, ctypes.byref(out)),
-                       "wtconv2d_workspace_bytes")
-            nbytes = self._ws_cache[key] = int(out.value)
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
-        with torch.cuda.device(x.device):
-            stream = torch.cuda.current_stream(x.device).cuda_stream
-            st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
-                                      ws.data_ptr() if ws is not None else None, nbytes,
-                                      B, C, H, W, K, L, s, code, xs, ys, stream)
-        _lib.check(st, "wtconv2d_forward")
-        return y
+        out = ctypes.c_size_t(0)
+        _lib.check(lib.wtconv2d_workspace_bytes(B, C, H, W, K, L, code, xs, ys, ctypes.byref(out)),
+                   "wtconv2d_workspace_bytes")
+        if len(self._call_cache) > 64:
+            self._call_cache.clear()
+        return (make_contiguous, out_shape, out_format, xs, ys, int(out.value), (B, C, H, W, K, L, s, code))
 
 
 class WTConv1d(_WTConvNd):
