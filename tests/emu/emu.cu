@@ -13,6 +13,7 @@
 #include "../../include/wtconv_b200.h"
 #include "../../wtconv_b200/csrc/wt1d_host.h"
 #include "../../wtconv_b200/csrc/wt2d_fused.cuh"
+#include "../../wtconv_b200/csrc/wt2d_quad.cuh"
 #include "../../wtconv_b200/csrc/wt2d_host.h"
 #include "../../wtconv_b200/csrc/wt_aux.h"
 
@@ -72,6 +73,25 @@ void run_regplane(const RegPlane& a, int dtype, const void* x, void* y, float* r
   else if (dtype == 0) run_regplane_t<float, true>(a, x, y, rout, packed);
   else if (dtype == 1) run_regplane_t<__nv_bfloat16, true>(a, x, y, rout, packed);
   else run_regplane_t<__half, true>(a, x, y, rout, packed);
+}
+
+// four-warp 14 x 14 level kernel
+template <typename T, bool BASE>
+void run_quad_t(const QuadPlane& a, const void* x, void* y, const float* rin, float* rout, const float* packed) {
+  const int floats = 32 * a.wpad + kQuadSmemFloats + 16;
+  AlignedBuf smem(floats);
+  for (int nb = 0; nb < a.nbatch; ++nb)
+    for (int cg = 0; cg < a.ngroups; ++cg) {
+      for (int i = 0; i < floats; ++i) smem.p[i] = 1.0e30f;
+      quad_cta<T, 5, BASE>(a, static_cast<const T*>(x), static_cast<T*>(y), rin, rout, packed, smem.p, cg, nb);
+    }
+}
+
+void run_quad(const QuadPlane& a, int dtype, const void* x, void* y, const float* rin, float* rout, const float* packed) {
+  if (!a.has_base) run_quad_t<float, false>(a, x, nullptr, rin, rout, packed);
+  else if (dtype == 0) run_quad_t<float, true>(a, x, y, rin, rout, packed);
+  else if (dtype == 1) run_quad_t<__nv_bfloat16, true>(a, x, y, rin, rout, packed);
+  else run_quad_t<__half, true>(a, x, y, rin, rout, packed);
 }
 
 template <typename T, int K>
@@ -168,16 +188,19 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
       }
     } else {
       const float* in = ws.data() + rd.in_off;
+      const long long s1 = rd.in_cl ? 1 : (long long)rd.Hin * rd.Win, s2 = rd.in_cl ? (long long)rd.Win * C : rd.Win,
+                      s3 = rd.in_cl ? C : 1;
       for (long long i = 0; i < total; ++i)
-        out[rd.out_cl ? reduce_cl_index(i, C, rd.Hout, rd.Wout) : i] = reduce_value<float>(in, i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift,
-                                     (long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1);
+        out[rd.out_cl ? reduce_cl_index(i, C, rd.Hout, rd.Wout) : i] =
+            reduce_value<float>(in, i, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, (long long)C * rd.Hin * rd.Win, s1, s2, s3);
     }
   }
   if (info) {
     info[0] = (int)ch.stages.size(); info[1] = (int)ch.reduces.size(); info[2] = ch.stages.back().plan.G;
     info[3] = (int)ch.stages.back().smem_bytes;
     info[4] = 0;
-    for (const Stage2d& sg : ch.stages) info[4] += sg.kind == 1;
+    info[5] = 0;
+    for (const Stage2d& sg : ch.stages) { info[4] += sg.kind == 1; info[5] += sg.kind == 2; }
   }
   for (const Stage2d& sg : ch.stages) {
     const bool from_x = sg.xin_off < 0;
@@ -188,6 +211,10 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
     const int dt = from_x ? dtype : 0;
     if (sg.kind == 1) {
       run_regplane(sg.reg, dt, xin, final_stage ? y : nullptr, rout, packed);
+      continue;
+    }
+    if (sg.kind == 2) {
+      run_quad(sg.quad, dt, xin, final_stage ? y : nullptr, rin, rout, packed);
       continue;
     }
     switch (K) {

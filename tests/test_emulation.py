@@ -80,6 +80,7 @@ def test_emulated_register_resident_bottom(B, C, H, W, L, dtype):
     packed = emu_lib.pack(params, 2, C, 5, L)
     y, info = emu_lib.forward2d(x, packed, 5, L)
     assert info[4] == 1, f"the register-resident stage was not planned: {info}"
+    assert info[5] == (1 if max(H, W) > 7 else 0), f"four-warp 14x14 stage: {info}"
     assert not torch.isnan(y.float()).any()
     tol = TOL[str(dtype).split(".")[1]]
     assert max_err(y.double().numpy(), ref) <= tol

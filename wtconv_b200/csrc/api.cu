@@ -231,7 +231,9 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     if (rd.in_off < 0) {
       e = launch_reduce(dtype, x, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout, rd.shift, ly.xs, rd.out_cl, cs);
     } else {
-      const long long s[4] = {(long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1};
+      const long long planar[4] = {(long long)C * rd.Hin * rd.Win, (long long)rd.Hin * rd.Win, rd.Win, 1};
+      const long long chlast[4] = {(long long)C * rd.Hin * rd.Win, 1, (long long)rd.Win * C, C};
+      const long long* s = rd.in_cl ? chlast : planar;
       e = launch_reduce(WTCONV_F32, ws + rd.in_off, ws + rd.out_off, B, C, rd.Hin, rd.Win, rd.Hout, rd.Wout,
                         rd.shift, s, rd.out_cl, cs);
     }
@@ -248,6 +250,9 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     switch (sg.kind) {
       case 1:
         e = launch_regplane(sg.reg, in_dtype, xin, final_stage ? y : nullptr, rout, packed, (size_t)sg.smem_bytes, cs);
+        break;
+      case 2:
+        e = launch_quad(sg.quad, in_dtype, xin, final_stage ? y : nullptr, rin, rout, packed, (size_t)sg.smem_bytes, cs);
         break;
       default:
         e = launch_wt2d(sg.plan, in_dtype, xin, final_stage ? y : nullptr, packed, rin, rout, (size_t)sg.smem_bytes, cs);

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "wt2d_plan.h"
+#include "wt2d_quad.cuh"
 #include "wt2d_regplane.cuh"
 
 namespace wt {
@@ -179,9 +180,46 @@ inline long long plan_regplane(RegPlane& a, int B, int C, int K, int L, int q, i
   return (long long)32 * a.wpad * 4;
 }
 
+// The four-warp level kernel handles planes of 13 or 14 rows / columns (7 x 7 sub-bands), K = 5
+inline bool quad_supported(int K, int H, int W) {
+  return K == 5 && (H == 13 || H == 14) && (W == 13 || W == 14);
+}
+
+// Launch description of the four-warp kernel for level q+1 on the Hp x Wp plane of level q.
+// q = 0: the layer itself (tensor strides xs / ys, base path included); q > 0: the plane set is
+// a channel-fastest fp32 reduction and the reconstruction is written as (B,C,Hp,Wp) planes.
+inline long long plan_quad(QuadPlane& a, int B, int C, int K, int L, int q, int Hp, int Wp, const long long* xs,
+                           const long long* ys) {
+  a = QuadPlane();
+  a.B = B; a.C = C; a.Hp = Hp; a.Wp = Wp; a.K = K; a.lvl0 = q;
+  a.has_base = (q == 0) ? 1 : 0;
+  a.has_rin = 1;
+  a.wstride = packed_channel_floats(K, 2, L);
+  const int ts = tapset_floats(K, 2);
+  a.wbeg = a.has_base ? 0 : ts * (1 + 4 * q);
+  a.wlen = ts * (a.has_base + 4);
+  a.wpad = a.wlen + (((a.wlen / 4) % 2 == 0) ? 4 : 0);
+  a.ngroups = cdiv(C, 32);
+  // about one wave of CTAs (three per SM): the tap sets are staged once per CTA
+  const long long tasks = (long long)B * a.ngroups;
+  a.samples_per_cta = (int)imax(1, (int)((tasks + 443) / 444));
+  a.nbatch = cdiv(B, a.samples_per_cta);
+  const long long chlast[4] = {(long long)C * Hp * Wp, 1, (long long)Wp * C, C};
+  const long long rcl[4] = {(long long)C * kQuadP * kQuadP, 1, (long long)kQuadP * C, C};
+  for (int i = 0; i < 4; ++i) {
+    a.xs[i] = (q == 0) ? xs[i] : chlast[i];
+    a.ys[i] = (q == 0) ? ys[i] : 0;
+    a.rs[i] = rcl[i];
+  }
+  return (long long)(32 * a.wpad + kQuadSmemFloats) * 4;
+}
+
 struct Stage2d {
-  int kind = 0;        // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg)
+  // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg),
+  // 2: four-warp 14 x 14 level kernel (quad)
+  int kind = 0;
   RegPlane reg;
+  QuadPlane quad;
   Plan2d plan = Plan2d();
   long long xin_off;   // fp32 low-pass planes read as input (floats into scratch), -1: the layer input
   long long rin_off;   // reconstruction of the deeper levels read, -1: none
@@ -194,7 +232,8 @@ struct Reduce2d {
   long long in_off;    // -1: the layer input
   long long out_off;
   int Hin, Win, Hout, Wout, shift;
-  int out_cl = 0;      // 1: the sums are stored channel-fastest, (B,Hout,Wout,C), for the register-resident stage
+  int out_cl = 0;      // 1: the sums are stored channel-fastest, (B,Hout,Wout,C)
+  int in_cl = 0;       // 1: the input is such a channel-fastest fp32 array in scratch
 };
 
 struct Chain2d {
@@ -336,8 +375,61 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     ch.stages.push_back(st);
     return ch;
   }
-  const int Ltop = qreg > 0 ? qreg : ly.L;     // levels handled by CTA-tile stages
-  const bool below = qreg > 0;                 // their deepest stage reads a reconstruction from below
+  // The level whose sub-bands are those 7 x 7 planes goes to the four-warp kernel.
+  int qquad = -1;
+  if (qreg >= 1 && tune.regplane >= 0 && quad_supported(ly.K, Hl[qreg - 1], Wl[qreg - 1]) &&
+      (qreg > 1 || (ly.stride == 1 && ly.ys[1] == 1)))
+    qquad = qreg - 1;
+  // Scratch of the register-level stages: low-pass planes (channel-fastest) and reconstructions
+  long long off = 0;
+  const long long n7 = qreg > 0 ? ((long long)ly.B * ly.C * Hl[qreg] * Wl[qreg] + 3) / 4 * 4 : 0;
+  const long long n14 = qquad >= 0 ? ((long long)ly.B * ly.C * Hl[qquad] * Wl[qquad] + 3) / 4 * 4 : 0;
+  long long x14_off = -1, x7_off = -1, r7_off = -1, r14_off = -1;
+  if (qquad > 0) { x14_off = off; off += n14; }
+  if (qreg > 0) { x7_off = off; off += n7; r7_off = off; off += n7; }
+  if (qquad > 0) { r14_off = off; off += n14; }
+  if (qreg > 0) {
+    if (qquad > 0) {                   // x -> 14 x 14 planes -> 7 x 7 planes
+      Reduce2d ra;
+      ra.in_off = -1; ra.out_off = x14_off;
+      ra.Hin = ly.H; ra.Win = ly.W; ra.Hout = Hl[qquad]; ra.Wout = Wl[qquad];
+      ra.shift = qquad; ra.out_cl = 1;
+      ch.reduces.push_back(ra);
+      Reduce2d rb;
+      rb.in_off = x14_off; rb.out_off = x7_off;
+      rb.Hin = Hl[qquad]; rb.Win = Wl[qquad]; rb.Hout = Hl[qreg]; rb.Wout = Wl[qreg];
+      rb.shift = 1; rb.out_cl = 1; rb.in_cl = 1;
+      ch.reduces.push_back(rb);
+    } else {                           // low-pass plane of level qreg straight from the layer input
+      Reduce2d rd;
+      rd.in_off = -1; rd.out_off = x7_off;
+      rd.Hin = ly.H; rd.Win = ly.W; rd.Hout = Hl[qreg]; rd.Wout = Wl[qreg];
+      rd.shift = qreg; rd.out_cl = 1;
+      ch.reduces.push_back(rd);
+    }
+    Stage2d st;
+    st.kind = 1;
+    st.smem_bytes = plan_regplane(st.reg, ly.B, ly.C, ly.K, ly.L, qreg, ly.L - qreg, Hl[qreg], Wl[qreg], nullptr,
+                                  nullptr, true);
+    if (qquad >= 0)                    // the four-warp kernel reads the reconstruction channel-fastest
+      for (int i = 0; i < 4; ++i) st.reg.os[i] = st.reg.xs[i];
+    st.xin_off = x7_off; st.rin_off = -1; st.rout_off = r7_off;
+    ch.stages.push_back(st);
+  }
+  if (qquad >= 0) {
+    Stage2d st;
+    st.kind = 2;
+    st.smem_bytes = plan_quad(st.quad, ly.B, ly.C, ly.K, ly.L, qquad, Hl[qquad], Wl[qquad], ly.xs, ly.ys);
+    st.xin_off = qquad == 0 ? -1 : x14_off;
+    st.rin_off = r7_off;
+    st.rout_off = qquad == 0 ? -1 : r14_off;
+    ch.stages.push_back(st);
+    if (qquad == 0) { ch.scratch_floats = off; return ch; }
+  }
+  const int qbelow = qquad > 0 ? qquad : qreg;   // level whose reconstruction the stages above read
+  const long long rbelow_off = qquad > 0 ? r14_off : r7_off;
+  const int Ltop = qbelow > 0 ? qbelow : ly.L;   // levels handled by CTA-tile stages
+  const bool below = qbelow > 0;                 // their deepest stage reads a reconstruction from below
 
   // top-down: decide the stage boundaries.  A stage is "whole" (its plane and every
   // deeper level stay on chip) or "tiled" (a few levels on halo tiles, the rest below).
@@ -367,22 +459,15 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     if (q == Ltop) break;   // also ends a base-only layer (nlev == 0)
   }
   // With exactly one deep CTA-tile stage it reads the layer input itself and forms its low-pass
-  // plane while loading; with more, the low-pass planes are materialised in scratch (as is
-  // the input of the register-resident stage).
+  // plane while loading; with more, the low-pass planes are materialised in scratch.
   const bool direct = (cuts.size() == 2);
-  long long off = 0;
   std::vector<long long> xoff(cuts.size(), -1), roff(cuts.size() + 1, -1);
   for (size_t i = 1; i < cuts.size(); ++i) {
     const long long n = (long long)ly.B * ly.C * Hl[cuts[i].first] * Wl[cuts[i].first];
     if (!direct) { xoff[i] = off; off += (n + 3) / 4 * 4; }
     roff[i] = off; off += (n + 3) / 4 * 4;
   }
-  long long reg_xoff = -1;
-  if (below) {
-    const long long n = (long long)ly.B * ly.C * Hl[qreg] * Wl[qreg];
-    reg_xoff = off; off += (n + 3) / 4 * 4;
-    roff[cuts.size()] = off; off += (n + 3) / 4 * 4;
-  }
+  roff[cuts.size()] = rbelow_off;
   ch.scratch_floats = off;
   if (!direct) {
     for (size_t i = 1; i < cuts.size(); ++i) {
@@ -394,21 +479,6 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
       rd.shift = to - from;
       ch.reduces.push_back(rd);
     }
-  }
-  if (below) {
-    Reduce2d rd;                      // low-pass plane of level qreg straight from the layer input
-    rd.in_off = -1;
-    rd.out_off = reg_xoff;
-    rd.Hin = ly.H; rd.Win = ly.W; rd.Hout = Hl[qreg]; rd.Wout = Wl[qreg];
-    rd.shift = qreg;
-    rd.out_cl = 1;
-    ch.reduces.push_back(rd);
-    Stage2d st;
-    st.kind = 1;
-    st.smem_bytes = plan_regplane(st.reg, ly.B, ly.C, ly.K, ly.L, qreg, ly.L - qreg, Hl[qreg], Wl[qreg],
-                                  nullptr, nullptr, true);
-    st.xin_off = reg_xoff; st.rin_off = -1; st.rout_off = roff[cuts.size()];
-    ch.stages.push_back(st);
   }
   for (int i = (int)cuts.size() - 1; i >= 0; --i) {
     Stage2d st;

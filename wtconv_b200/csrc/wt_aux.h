@@ -12,6 +12,7 @@ namespace wt {
 struct Plan2d;
 struct Plan1d;
 struct RegPlane;
+struct QuadPlane;
 
 struct PackArgs {
   int C, L, taps, tapset, subbands;
@@ -103,6 +104,9 @@ cudaError_t launch_wt2d_k(const Plan2d& p, int dtype, const void* x, void* y, co
 
 cudaError_t launch_regplane(const RegPlane& a, int dtype, const void* x, void* y, float* rout,
                             const float* packed, size_t smem_bytes, cudaStream_t stream);
+
+cudaError_t launch_quad(const QuadPlane& a, int dtype, const void* x, void* y, const float* rin, float* rout,
+                        const float* packed, size_t smem_bytes, cudaStream_t stream);
 
 template <int K>
 cudaError_t launch_wt1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* packed,
