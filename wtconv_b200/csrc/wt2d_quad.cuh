@@ -18,8 +18,9 @@
 // In component form a K x K 'same' convolution of the plane is a sum over the four source
 // components of small convolutions with shifts -1, 0, +1; which tap belongs to a shift
 // depends on the parity of the warp's own component, so the taps are fetched from shared
-// memory with a computed index (zero weight when the tap does not exist).  One code path
-// for all four warps keeps the kernel small enough for the instruction cache.
+// memory with a computed index and shifts without a tap are skipped by a branch that is
+// uniform over the warp.  One code path for all four warps keeps the kernel small enough
+// for the instruction cache.
 #pragma once
 
 #include "wt2d_regplane.cuh"
@@ -161,7 +162,7 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
 #pragma unroll
           for (int j = 0; j < P; ++j) acc[i][j] = bias;
         // source component (py,px), shifted by (su,sv): source pixel row 2(i+su)+py must equal
-        // 2i+di+ky-r, i.e. ky = 2su + py - di + r (likewise kx); no such tap -> weight 0
+        // 2i+di+ky-r, i.e. ky = 2su + py - di + r (likewise kx); no such tap -> nothing to add
 #pragma unroll
         for (int comp = 0; comp < 4; ++comp) {
           const int py = comp >> 1, px = comp & 1;
@@ -178,8 +179,8 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
 #pragma unroll
             for (int sv = -1; sv <= 1; ++sv) {
               const int kx = 2 * sv + px - dj + r;
-              const bool ok = kyok && kx >= 0 && kx < K;
-              const float wv = ok ? w[imin(imax(ky, 0), K - 1) * K + imin(imax(kx, 0), K - 1)] : 0.f;
+              if (!(kyok && kx >= 0 && kx < K)) continue;       // uniform over the warp
+              const float wv = w[ky * K + kx];
 #pragma unroll
               for (int i = 0; i < P; ++i) {
                 if (i + su < 0 || i + su >= P) continue;
