@@ -309,7 +309,7 @@ struct Tuning2d {
   int tile_levels = 0;   // levels fused per tiled stage
   int group = 0;         // channels per CTA
   int threads = 0;       // threads per CTA
-  int regplane = 0;      // -1: never use the register-resident small-plane kernel
+  int regplane = 0;      // -1: never use the register-level kernels at the bottom; 1: also with other overrides
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -359,7 +359,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
   int qreg = -1;
   const bool untuned = !tune.force_tiled && !tune.tile_y && !tune.tile_x && !tune.tile_levels && !tune.group;
-  if (untuned && tune.regplane >= 0 && ly.xs[1] == 1 && ly.C > 1) {
+  if ((untuned || tune.regplane > 0) && tune.regplane >= 0 && ly.xs[1] == 1 && ly.C > 1) {
     for (int q = 0; q < ly.L; ++q) {
       if (!regplane_supported(ly.K, Hl[q], Wl[q], ly.L - q)) continue;
       if (q == 0 && (ly.stride != 1 || ly.ys[1] != 1)) continue;
