@@ -32,12 +32,6 @@
 
 #include "wt2d_plan.h"
 
-#ifndef WT_SKIP_MASK
-#define WT_SKIP_MASK 0
-#endif
-#ifndef WT_MARK
-#define WT_MARK(k)
-#endif
 namespace wt {
 
 template <bool B, typename A, typename C> struct Select { typedef A type; };
@@ -688,7 +682,6 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   Smem2d sm{smem, &p};
   T* out_tile = reinterpret_cast<T*>(smem + p.ooff);
 
-  WT_MARK(0)
   // ---- phase 0: stage the tap sets this stage uses, the input tile and the deeper reconstruction
   WT_PHASE(nthr) {
     {
@@ -713,9 +706,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       move_plane_rows<true>(rb, Hd * Wd, Wd, smem + p.roff[d], p.rplane[d], p.rpitch[d], gc, dy.n, dx.n, vec_ok,
                             tid, nthr);
     }
-    WT_MARK(6)
     // input tile -> X0; everything the tile does not take from the plane is zero
-    if (WT_SKIP_MASK & 1) continue;
     const LevelGeo gy = tg.y(0), gx = tg.x(0);
     FillRange fr;
     fr.ylo = imax(gy.lo, 0); fr.yhi = imin(gy.hi, p.H);
@@ -735,26 +726,21 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     } else {
       fill_x0_planar<T, XT>(p, xb, x0arr, fr, gc, tid, nthr);
     }
-    WT_MARK(7)
     async_wait_all();
   }
 
-  WT_MARK(1)
   // ---- phase 1: Haar analysis, level by level (wavelet.py:62-67; raw LL feeds the next level)
   for (int j = 1; j <= d; ++j) {
     WT_PHASE(nthr) {
-      if (WT_SKIP_MASK & 2) continue;
       const int oy = tg.y(j).org, ox = tg.x(j).org, soy = tg.y(j - 1).org, sox = tg.x(j - 1).org;
       if (j == 1) analysis_level<K, XT>(p, sm, 1, oy, ox, soy, sox, sm.x0<XT>(0), p.plane[0], gc, tid, nthr);
       else analysis_level<K, float>(p, sm, j, oy, ox, soy, sox, sm.sub(j - 1, 0, 0), p.plane[j - 1], gc, tid, nthr);
     }
   }
 
-  WT_MARK(2)
   // ---- phase 2: deep levels bottom-up: per-sub-band convolutions into Y, then the
   //      low-pass accumulation and synthesis butterfly into R_{j-1}
   for (int j = d; j >= 2; --j) {
-    if (WT_SKIP_MASK & 4) break;
     WT_PHASE(nthr) {
       const LevelGeo ly = tg.y(j), lx = tg.x(j);
       const int th = p.th[j];
@@ -810,11 +796,9 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
-  WT_MARK(3)
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
-    if (WT_SKIP_MASK & 8) continue;
     const LevelGeo y0 = tg.y(0), x0g = tg.x(0);
     if (d >= 1) {
       const LevelGeo y1 = tg.y(1), x1 = tg.x(1);
@@ -847,10 +831,8 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
-  WT_MARK(4)
   // ---- phase 4: write the tile
   WT_PHASE(nthr) {
-    if (WT_SKIP_MASK & 16) continue;
     const int hn = tg.ty1 - tg.ty0, wn = tg.tx1 - tg.tx0;
     if (!FINAL) {
       float* ob = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)tg.ty0 * p.W + tg.tx0;
@@ -873,7 +855,6 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
       }
     }
   }
-  WT_MARK(5)
 }
 
 }  // namespace wt
