@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted::
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path of the BGU-CS-VIL/WTConv checkout>
 
 The reference package ``wtconv`` is imported UNCHANGED from that path (only the
 table-only ``pywt`` stand-in in ``oracle/pywt_stub`` is put in front of it,
@@ -60,7 +60,7 @@ def build(ref_mod, ndim, c, k, levels, stride, bias, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout (read only)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(ROOT, "oracle", "pywt_stub"))
     sys.path.insert(0, args.reference)

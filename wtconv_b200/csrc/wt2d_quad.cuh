@@ -91,19 +91,33 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
       const T* xp = x + (long long)n * a.xs[0] + (long long)c * a.xs[1];
       const int xs2 = (int)a.xs[2], xs3 = (int)a.xs[3];
       T raw[P][P];
-#pragma unroll
-      for (int i = 0; i < P; ++i)
-#pragma unroll
-        for (int j = 0; j < P; ++j)
-          raw[i][j] = xp[imin(2 * i + di, a.Hp - 1) * xs2 + imin(2 * j + dj, a.Wp - 1) * xs3];
       float* dst = XS + q * kQuadCells + lane;
+      if (a.Hp == 2 * P && a.Wp == 2 * P) {
+        // full 14 x 14 plane: no clamping, the component is a plain strided view
+        const T* xq = xp + di * xs2 + dj * xs3;
+        const int rs = 2 * xs2, cs = 2 * xs3;
 #pragma unroll
-      for (int i = 0; i < P; ++i)
+        for (int i = 0; i < P; ++i)
 #pragma unroll
-        for (int j = 0; j < P; ++j) {
-          const bool ok = 2 * i + di < a.Hp && 2 * j + dj < a.Wp;     // zero extension of odd sizes
-          dst[(i * P + j) * 32] = ok ? Elem<T>::to_f(raw[i][j]) : 0.f;
-        }
+          for (int j = 0; j < P; ++j) raw[i][j] = xq[i * rs + j * cs];
+#pragma unroll
+        for (int i = 0; i < P; ++i)
+#pragma unroll
+          for (int j = 0; j < P; ++j) dst[(i * P + j) * 32] = Elem<T>::to_f(raw[i][j]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < P; ++i)
+#pragma unroll
+          for (int j = 0; j < P; ++j)
+            raw[i][j] = xp[imin(2 * i + di, a.Hp - 1) * xs2 + imin(2 * j + dj, a.Wp - 1) * xs3];
+#pragma unroll
+        for (int i = 0; i < P; ++i)
+#pragma unroll
+          for (int j = 0; j < P; ++j) {
+            const bool ok = 2 * i + di < a.Hp && 2 * j + dj < a.Wp;     // zero extension of odd sizes
+            dst[(i * P + j) * 32] = ok ? Elem<T>::to_f(raw[i][j]) : 0.f;
+          }
+      }
       if (a.has_rin) {
         const float* rp = rin + (long long)n * a.rs[0] + (long long)c * a.rs[1];
         const int rs2 = (int)a.rs[2], rs3 = (int)a.rs[3];
@@ -212,12 +226,21 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
         if constexpr (BASE) {
           T* yp = y + (long long)n * a.ys[0] + (long long)c * a.ys[1];
           const int ys2 = (int)a.ys[2], ys3 = (int)a.ys[3];
+          if (a.Hp == 2 * P && a.Wp == 2 * P) {
+            T* yq = yp + di * ys2 + dj * ys3;
+            const int rs = 2 * ys2, cs = 2 * ys3;
 #pragma unroll
-          for (int i = 0; i < P; ++i)
+            for (int i = 0; i < P; ++i)
 #pragma unroll
-            for (int j = 0; j < P; ++j)
-              if (2 * i + di < a.Hp && 2 * j + dj < a.Wp)
-                yp[(2 * i + di) * ys2 + (2 * j + dj) * ys3] = Elem<T>::from_f(acc[i][j]);
+              for (int j = 0; j < P; ++j) yq[i * rs + j * cs] = Elem<T>::from_f(acc[i][j]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < P; ++i)
+#pragma unroll
+              for (int j = 0; j < P; ++j)
+                if (2 * i + di < a.Hp && 2 * j + dj < a.Wp)
+                  yp[(2 * i + di) * ys2 + (2 * j + dj) * ys3] = Elem<T>::from_f(acc[i][j]);
+          }
         }
       }
       if constexpr (!BASE) {
