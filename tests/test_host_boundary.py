@@ -44,6 +44,30 @@ def test_host_only_entry_points():
     assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, None, None, ctypes.byref(nbytes)) == -2
 
 
+def test_launch_chains_of_the_benchmark_shapes():
+    """Planner through the C ABI (host only): channels-last WTConvNeXt stage shapes end in the
+    register-level kernels, NCHW and other kernel sizes stay on the CTA-tile stages."""
+    L = _lib()
+    lib = L.load()
+
+    def count(B, C, H, K, Lv, code, channels_last, stride=1):
+        st = (ctypes.c_longlong * 4)(*((C * H * H, 1, H * C, C) if channels_last else (C * H * H, H * H, H, 1)))
+        n = ctypes.c_int(-1)
+        assert lib.wtconv2d_launch_count(B, C, H, H, K, Lv, stride, code, st, st, ctypes.byref(n)) == 0
+        return n.value
+
+    # bf16 channels-last: regplane | reduce, regplane, quad | + reduce, final | + deep
+    assert [count(128, C, H, 5, Lv, 1, True) for C, H, Lv in
+            ((768, 7, 2), (384, 14, 3), (192, 28, 4), (96, 56, 5))] == [1, 3, 5, 6]
+    assert count(128, 768, 7, 5, 2, 1, False) == 1          # NCHW: one whole-plane CTA-tile stage
+    assert count(128, 96, 56, 5, 5, 1, False) == 1          # NCHW: the 56x56 pyramid still fits on chip
+    assert count(2, 256, 512, 5, 5, 1, False) >= 4          # 512x512: reductions and a chain of tiled stages
+    assert count(128, 768, 7, 3, 2, 1, True) == 1           # K = 3 has no register-level instance
+    assert count(4, 16, 7, 5, 2, 0, True, stride=2) == 1    # strided output: CTA-tile stage
+    n = ctypes.c_int(0)
+    assert lib.wtconv2d_launch_count(1, 8, 8, 8, 4, 1, 1, 0, None, None, ctypes.byref(n)) == -2   # even K
+
+
 @pytest.mark.parametrize("name", golden_names())
 def test_state_dict_matches_reference_layout(name):
     import wtconv_b200
