@@ -133,7 +133,7 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
       for (int i = 0; i < P; ++i)
 #pragma unroll
         for (int j = 0; j < P; ++j) S[i][j] = 0.f;
-#pragma unroll
+#pragma unroll 1                                   // rolled: four times less code to fetch
       for (int comp = 0; comp < 4; ++comp) {
         const float sg = quad_sign(s, comp >> 1, comp & 1);
         const float* src = XS + comp * kQuadCells + lane;
@@ -177,7 +177,7 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
           for (int j = 0; j < P; ++j) acc[i][j] = bias;
         // source component (py,px), shifted by (su,sv): source pixel row 2(i+su)+py must equal
         // 2i+di+ky-r, i.e. ky = 2su + py - di + r (likewise kx); no such tap -> nothing to add
-#pragma unroll
+#pragma unroll 1
         for (int comp = 0; comp < 4; ++comp) {
           const int py = comp >> 1, px = comp & 1;
           const float* src = XS + comp * kQuadCells + lane;
@@ -213,7 +213,7 @@ WT_HD void quad_cta(const QuadPlane& a, const T* __restrict__ x, T* __restrict__
 #pragma unroll
           for (int j = 0; j < P; ++j) acc[i][j] = 0.f;
       }
-#pragma unroll
+#pragma unroll 1
       for (int s = 0; s < 4; ++s) {
         const float sg = quad_sign(s, di, dj);
         const float* src = YS + s * kQuadCells + lane;
