@@ -91,6 +91,23 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype,
                        float* packed, void* stream);
 
 /*
+ * Same block as wtconv_pack_params, for the ADJOINT of the layer: every tap set
+ * is reversed (the K x K kernels flipped in both directions) and the bias slot
+ * is zero.  The Haar transform is orthogonal and the reference pads / crops odd
+ * sizes symmetrically (wtconv/wtconv2d.py:49-51,76), so running
+ * wtconv2d_forward / wtconv1d_forward (stride 1) with this block on the
+ * gradient of the output gives the gradient of the input -- what autograd
+ * computes for wtconv/wtconv2d.py:38-87 and what the reference CUDA backend
+ * computes in fused_haar_conv_scale_bwd (fast_wtconv/cuda_haar/
+ * fused_haar_conv.cu:148-234).  Parameter gradients are not provided.
+ */
+int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype,
+                       double ana_tap, double syn_tap,
+                       const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale,
+                       float* packed, void* stream);
+
+/*
  * Scratch bytes wtconv2d_forward needs for this problem and memory layout (0
  * when the whole cascade of a plane is fused on chip, which is the case for
  * small planes; larger planes hand the reconstruction of their deep levels --

@@ -125,9 +125,9 @@ extern "C" {
 
 int emu_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
                     const void* base_w, const void* base_b, const void* base_scale, const void* const* wavelet_w,
-                    const void* const* wavelet_scale, float* packed) {
+                    const void* const* wavelet_scale, float* packed, int adjoint) {
   PackArgs a;
-  a.C = C; a.L = L;
+  a.C = C; a.L = L; a.adjoint = adjoint;
   a.taps = (ndim == 2) ? K * K : K;
   a.tapset = tapset_floats(K, ndim);
   a.subbands = (ndim == 2) ? 4 : 2;

@@ -61,7 +61,7 @@ def taps(ndim, dtype):
     return float(t), float(t)
 
 
-def pack(params, ndim, C, K, L, param_dtype=torch.float32, filter_dtype=None):
+def pack(params, ndim, C, K, L, param_dtype=torch.float32, filter_dtype=None, adjoint=False):
     p = {k: v.to(param_dtype).contiguous() for k, v in params.items()}
     sub = 4 if ndim == 2 else 2
     n = C * ((K ** ndim + 1 + 3) // 4 * 4) * (1 + sub * L)
@@ -71,7 +71,7 @@ def pack(params, ndim, C, K, L, param_dtype=torch.float32, filter_dtype=None):
     ana, syn = taps(ndim, filter_dtype or param_dtype)
     st = lib().emu_pack_params(ndim, C, K, L, DTYPE_CODE[param_dtype], ctypes.c_double(ana), ctypes.c_double(syn),
                                _ptr(p["base_conv.weight"]), _ptr(p.get("base_conv.bias")),
-                               _ptr(p["base_scale.weight"]), ww, ws, _ptr(packed))
+                               _ptr(p["base_scale.weight"]), ww, ws, _ptr(packed), int(adjoint))
     assert st == 0
     return packed
 

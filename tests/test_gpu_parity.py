@@ -370,5 +370,39 @@ def test_c_abi_error_codes():
         m(x)
     m = wtconv_b200.WTConv2d(4, 4, kernel_size=5, wt_levels=1).to(dev)
     with pytest.raises(NotImplementedError):
-        m(x)                                     # grad mode with trainable parameters: forward-only
+        m(x)                                     # grad mode with trainable parameters: not implemented
     torch.cuda.synchronize()
+
+
+# Gradient of the input (frozen parameters): the adjoint of the layer is the layer with flipped
+# kernels and no bias, run by the same CUDA kernels; checked against autograd through the oracle.
+@pytest.mark.parametrize("ndim,shape,L,K,stride,layout,dtype", [
+    (2, (2, 8, 56, 56), 5, 5, 1, "cl", torch.float32), (2, (3, 40, 14, 13), 3, 5, 1, "cl", torch.float32),
+    (2, (2, 6, 21, 30), 3, 3, 1, "nchw", torch.float32), (2, (2, 4, 17, 16), 2, 5, 2, "nchw", torch.float32),
+    (2, (2, 16, 7, 7), 2, 5, 1, "cl", torch.bfloat16), (2, (1, 4, 150, 90), 4, 7, 1, "cl", torch.float32),
+    (1, (2, 6, 515), 4, 5, 1, "nchw", torch.float32), (1, (2, 4, 100), 3, 3, 2, "nchw", torch.float32),
+])
+def test_input_gradient(ndim, shape, L, K, stride, layout, dtype):
+    dev = _cuda()
+    C = shape[1]
+    params = wtconv_torch.random_params(C, K, L, ndim=ndim, bias=True, seed=sum(shape))
+    g = torch.Generator().manual_seed(shape[-1])
+    x = torch.randn(shape, generator=g)
+    m = _module(ndim, C, K, L, stride, True, params, dtype, dev)
+    for p in m.parameters():
+        p.requires_grad_(False)
+    xt = x.to(dev).to(dtype)
+    if layout == "cl":
+        xt = xt.contiguous(memory_format=torch.channels_last)
+    xt.requires_grad_(True)
+    y = m(xt)
+    gy = torch.randn(y.shape, generator=g)
+    (gx,) = torch.autograd.grad(y, xt, gy.to(dev).to(dtype))
+    # oracle: autograd through the reference operator sequence in fp64
+    xr = x.to(dtype).double().requires_grad_(True)
+    fn = wtconv_torch.wtconv2d_forward if ndim == 2 else wtconv_torch.wtconv1d_forward
+    yr = fn(xr, {k: torch.as_tensor(v).to(dtype).double() for k, v in params.items() if "filter" not in k}, stride=stride)
+    (gr,) = torch.autograd.grad(yr, xr, gy.to(dtype).double())
+    assert tuple(gx.shape) == tuple(x.shape)
+    assert max_err(y.detach().float().cpu().numpy(), yr.detach().numpy()) <= TOL[dtype]
+    assert max_err(gx.float().cpu().numpy(), gr.numpy()) <= TOL[dtype]

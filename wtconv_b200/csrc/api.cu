@@ -154,7 +154,7 @@ size_t wtconv_packed_param_floats(int ndim, int C, int K, int L) {
   return (size_t)C * packed_channel_floats(K, ndim, L);
 }
 
-int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+static int pack_params_impl(int adjoint, int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
                        const void* base_w, const void* base_b, const void* base_scale,
                        const void* const* wavelet_w, const void* const* wavelet_scale, float* packed,
                        void* stream) {
@@ -163,7 +163,7 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double an
   if (st) return st;
   if (!base_w || !base_scale || !packed || (L > 0 && (!wavelet_w || !wavelet_scale))) return WTCONV_ERR_BAD_ARG;
   PackArgs a;
-  a.C = C; a.L = L;
+  a.C = C; a.L = L; a.adjoint = adjoint;
   a.taps = (ndim == 2) ? K * K : K;
   a.tapset = tapset_floats(K, ndim);
   a.subbands = (ndim == 2) ? 4 : 2;
@@ -180,6 +180,22 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double an
     a.gain[l] = g;
   }
   return (int)launch_pack(a, param_dtype, packed, static_cast<cudaStream_t>(stream));
+}
+
+int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                       const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale, float* packed,
+                       void* stream) {
+  return pack_params_impl(0, ndim, C, K, L, param_dtype, ana_tap, syn_tap, base_w, base_b, base_scale, wavelet_w,
+                          wavelet_scale, packed, stream);
+}
+
+int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                               const void* base_w, const void* base_b, const void* base_scale,
+                               const void* const* wavelet_w, const void* const* wavelet_scale, float* packed,
+                               void* stream) {
+  return pack_params_impl(1, ndim, C, K, L, param_dtype, ana_tap, syn_tap, base_w, base_b, base_scale, wavelet_w,
+                          wavelet_scale, packed, stream);
 }
 
 int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, const long long* x_strides,

@@ -22,6 +22,7 @@ struct PackArgs {
   const void* wavelet_w[kMaxLevels];
   const void* wavelet_scale[kMaxLevels];
   double gain[kMaxLevels];   // (analysis tap * synthesis tap)^(level+1)
+  int adjoint;               // 1: reversed tap sets and no bias (block of the adjoint layer)
 };
 
 // Value of packed float `i`.  Layout per channel c (ts = tap-set floats):
@@ -36,13 +37,16 @@ WT_HD float pack_value(const PackArgs& a, long long i) {
   const int per_c = ts * (1 + sub * a.L);
   const int c = (int)(i / per_c);
   const int rem = (int)(i - (long long)c * per_c);
-  const int set = rem / ts, k = rem - set * ts;
+  const int set = rem / ts;
+  int k = rem - set * ts;
+  const bool is_tap = k < taps;
+  if (a.adjoint && is_tap) k = taps - 1 - k;          // reversed taps = kernel flipped in every direction
   float v = 0.f;
   if (set == 0) {
     const float sc = Elem<P>::to_f(static_cast<const P*>(a.base_scale)[c]);
-    if (k < taps) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_w)[(size_t)c * taps + k]);
-    else if (k == taps && a.base_b) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_b)[c]);
-  } else if (k < taps) {
+    if (is_tap) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_w)[(size_t)c * taps + k]);
+    else if (k == taps && a.base_b && !a.adjoint) v = sc * Elem<P>::to_f(static_cast<const P*>(a.base_b)[c]);
+  } else if (is_tap) {
     const int l = (set - 1) / sub, s = (set - 1) - l * sub;
     const int oc = sub * c + s;
     const float sc = Elem<P>::to_f(static_cast<const P*>(a.wavelet_scale[l])[oc]);

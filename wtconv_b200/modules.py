@@ -102,8 +102,8 @@ class _WTConvNd(nn.Module):
         else:
             self.do_stride = None
 
-        self._packed = None
-        self._packed_key = None
+        self._packed = {}
+        self._packed_key = {}
         self._call_cache = {}
 
     # -- parameter folding -------------------------------------------------
@@ -113,14 +113,15 @@ class _WTConvNd(nn.Module):
             ps += [conv.weight, sc.weight]
         return ps
 
-    def _packed_params(self, device):
-        """fp32 block of folded parameters, rebuilt only when a parameter changed
-        (data pointer, in-place version counter, dtype or device)."""
+    def _packed_params(self, device, adjoint=False):
+        """fp32 block of folded parameters (or of the adjoint layer: flipped taps, no bias), rebuilt
+        only when a parameter changed (data pointer, in-place version counter, dtype or device)."""
         ps = self._kernel_params()
         key = tuple((p.data_ptr(), p._version) if p is not None else None for p in ps) \
             + (ps[0].dtype, ps[0].device, self.wt_filter.dtype)
-        if self._packed is not None and key == self._packed_key and self._packed.device == device:
-            return self._packed
+        cached = self._packed.get(adjoint)
+        if cached is not None and key == self._packed_key.get(adjoint) and cached.device == device:
+            return cached
         lib = _lib.load()
         real = [p for p in ps if p is not None]
         pdt = real[0].dtype
@@ -142,11 +143,12 @@ class _WTConvNd(nn.Module):
         ws = arr_t(*[hold[4 + 2 * i].data_ptr() for i in range(L)])
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream(device).cuda_stream
-            st = lib.wtconv_pack_params(nd, C, K, L, _DTYPE_CODE[pdt], tap, tap,
-                                        hold[0].data_ptr(), hold[1].data_ptr() if hold[1] is not None else None,
-                                        hold[2].data_ptr(), ww, ws, packed.data_ptr(), stream)
+            pack = lib.wtconv_pack_params_adjoint if adjoint else lib.wtconv_pack_params
+            st = pack(nd, C, K, L, _DTYPE_CODE[pdt], tap, tap,
+                      hold[0].data_ptr(), hold[1].data_ptr() if hold[1] is not None else None,
+                      hold[2].data_ptr(), ww, ws, packed.data_ptr(), stream)
         _lib.check(st, "wtconv_pack_params")
-        self._packed, self._packed_key = packed, key
+        self._packed[adjoint], self._packed_key[adjoint] = packed, key
         return packed
 
     def _check_input(self, x):
@@ -156,36 +158,74 @@ class _WTConvNd(nn.Module):
             raise TypeError(f"unsupported activation dtype {x.dtype}; use float32, bfloat16 or float16")
         if x.dim() != self._ndim + 2 or x.shape[1] != self.in_channels:
             raise ValueError(f"expected a {self._ndim + 2}-D input with {self.in_channels} channels, got {tuple(x.shape)}")
-        if torch.is_grad_enabled() and (x.requires_grad or any(
-                p is not None and p.requires_grad for p in self._kernel_params())):
+        if torch.is_grad_enabled() and any(p is not None and p.requires_grad for p in self._kernel_params()):
             raise NotImplementedError(
-                "wtconv_b200 implements the forward pass only: call it under torch.no_grad() / "
-                "torch.inference_mode() (no autograd graph is recorded)")
+                "wtconv_b200 computes the forward pass and the gradient of the input only: parameter "
+                "gradients are not implemented. Freeze the parameters (requires_grad_(False)) or call the "
+                "layer under torch.no_grad() / torch.inference_mode()")
+
+    def forward(self, x):
+        self._check_input(x)
+        if torch.is_grad_enabled() and x.requires_grad:
+            return _InputGradFunction.apply(x, self)
+        return self._run(x)
+
+    def _grad_to_full_resolution(self, gy, in_shape):
+        """Adjoint of the output stride: the gradient of the layer output before the stride."""
+        s = self.stride
+        if s == 1:
+            return gy
+        full = gy.new_zeros(in_shape)
+        if self._ndim == 2:
+            full[..., ::s, ::s] = gy                       # wtconv2d.py:33-34: AvgPool2d(1, s) picks samples
+        else:
+            n = gy.shape[-1] * s                            # wtconv1d.py:34: AvgPool1d(s, s) averages s samples
+            full[..., :n] = gy.repeat_interleave(s, dim=-1) / s
+        return full
+
+
+class _InputGradFunction(torch.autograd.Function):
+    """Records the layer in the autograd graph with respect to its input only.  The Haar transform
+    is orthogonal and odd sizes are padded and cropped at the same places, so the adjoint of the
+    layer is the layer itself with every kernel flipped and the bias dropped: the backward pass is
+    one more forward call on the gradient, with the adjoint parameter block."""
+
+    @staticmethod
+    def forward(ctx, x, module):
+        ctx.module = module
+        ctx.in_shape = x.shape
+        return module._run(x)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gy):
+        m = ctx.module
+        g = m._grad_to_full_resolution(gy, ctx.in_shape)
+        return m._run(g, adjoint=True, stride=1), None
 
 
 class WTConv2d(_WTConvNd):
     """Wavelet convolution layer, forward on B200 (reference: wtconv/wtconv2d.py:8-87)."""
     _ndim = 2
 
-    def forward(self, x):
-        self._check_input(x)
+    def _run(self, x, adjoint=False, stride=None):
         lib = _lib.load()
         dev = x.device
+        s = self.stride if stride is None else stride
         # everything that depends only on the geometry of the call is computed once per
-        # (shape, strides, dtype): output layout, ctypes stride arrays, scratch size
-        key = (tuple(x.shape), x.stride(), x.dtype)
+        # (shape, strides, dtype, stride): output layout, ctypes stride arrays, scratch size
+        key = (tuple(x.shape), x.stride(), x.dtype, s)
         rec = self._call_cache.get(key)
         if rec is None:
-            rec = self._call_cache[key] = self._plan_call(lib, x)
+            rec = self._call_cache[key] = self._plan_call(lib, x, s)
         if rec is _EMPTY:
             B, C, H, W = x.shape
-            s = self.stride
             return x.new_empty((B, C, -(-H // s), -(-W // s)))
         make_contiguous, out_shape, out_format, xs, ys, nbytes, dims = rec
         if make_contiguous:
             x = x.contiguous()
         y = torch.empty(out_shape, dtype=x.dtype, device=dev, memory_format=out_format)
-        packed = self._packed_params(dev)
+        packed = self._packed_params(dev, adjoint)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
         if torch.cuda.current_device() == dev.index:
             st = lib.wtconv2d_forward(x.data_ptr(), y.data_ptr(), packed.data_ptr(),
@@ -200,9 +240,8 @@ class WTConv2d(_WTConvNd):
             _lib.check(st, "wtconv2d_forward")
         return y
 
-    def _plan_call(self, lib, x):
+    def _plan_call(self, lib, x, s):
         B, C, H, W = x.shape
-        s = self.stride
         if x.numel() == 0:
             return _EMPTY
         channels_last = x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()
@@ -227,17 +266,16 @@ class WTConv1d(_WTConvNd):
     """1-D wavelet convolution layer, forward on B200 (reference: wtconv/wtconv1d.py:8-87)."""
     _ndim = 1
 
-    def forward(self, x):
-        self._check_input(x)
+    def _run(self, x, adjoint=False, stride=None):
         lib = _lib.load()
         B, C, N = x.shape
-        s = self.stride
+        s = self.stride if stride is None else stride
         y = torch.empty((B, C, N // s), dtype=x.dtype, device=x.device)
         if y.numel() == 0:
             return y
         if x.stride(2) != 1:
             x = x.contiguous()
-        packed = self._packed_params(x.device)
+        packed = self._packed_params(x.device, adjoint)
         xs = (ctypes.c_longlong * 3)(*x.stride())
         ys = (ctypes.c_longlong * 3)(*y.stride())
         with torch.cuda.device(x.device):
