@@ -108,6 +108,37 @@ int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype,
                        float* packed, void* stream);
 
 /*
+ * Parameter gradients of WTConv2d (the weight-gradient half of the backward
+ * pass; the input gradient is wtconv2d_forward on wtconv_pack_params_adjoint's
+ * block).  The reference gets them from autograd through
+ * wtconv/wtconv2d.py:46-85; its CUDA backend from
+ * fused_haar_grad_weight_kernel and depthwise_grad_weight_kernel
+ * (fast_wtconv/cuda_haar/fused_haar_conv.cu:257-342, depthwise_grad.cu:32-101).
+ *
+ * wtconv2d_pyramid writes the un-normalised Haar sub-bands of every level of a
+ * tensor (x, or the gradient of the output at full resolution): level l as
+ * fp32 (B, H_l, W_l, 4, C), levels concatenated, wtconv2d_pyramid_floats()
+ * floats in all.  wtconv2d_weight_grad_stats then fills
+ * stats[(1+4L)][K*K+1][C] (wtconv2d_weight_grad_stat_floats() floats; zeroed by
+ * the call): for set 0 (base) and sets 1+4l+s (level l, sub-band s) the K x K
+ * correlation sums between the two pyramids and, in slot K*K, the plain sum of
+ * the gradient plane.  Per channel,
+ *   d base_conv.weight = base_scale * stats[0],  d base_conv.bias = base_scale * stats[0][K*K],
+ *   d base_scale = <base_conv.weight, stats[0]> + bias * stats[0][K*K],
+ *   d wavelet_convs[l].weight[4c+s] = wavelet_scale[l][4c+s] * g_l * stats[1+4l+s],
+ *   d wavelet_scale[l][4c+s] = g_l * <wavelet_convs[l].weight[4c+s], stats[1+4l+s]>,
+ * with g_l = (ana_tap * syn_tap)^(l+1).  Sums are accumulated with floating-point
+ * atomics (order not fixed, like the reference's kernels).
+ */
+size_t wtconv2d_pyramid_floats(int B, int C, int H, int W, int L);
+int wtconv2d_pyramid(const void* t, float* pyramid, int B, int C, int H, int W, int L, int dtype,
+                     const long long* strides, void* stream);
+size_t wtconv2d_weight_grad_stat_floats(int C, int K, int L);
+int wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x_pyramid, const float* g_pyramid,
+                               float* stats, int B, int C, int H, int W, int K, int L, int dtype,
+                               const long long* x_strides, const long long* g_strides, void* stream);
+
+/*
  * Scratch bytes wtconv2d_forward needs for this problem and memory layout (0
  * when the whole cascade of a plane is fused on chip, which is the case for
  * small planes; larger planes hand the reconstruction of their deep levels --

@@ -14,6 +14,7 @@
 #include "../../wtconv_b200/csrc/wt1d_host.h"
 #include "../../wtconv_b200/csrc/wt2d_fused.cuh"
 #include "../../wtconv_b200/csrc/wt2d_quad.cuh"
+#include "../../wtconv_b200/csrc/wt2d_wgrad.cuh"
 #include "../../wtconv_b200/csrc/wt2d_host.h"
 #include "../../wtconv_b200/csrc/wt_aux.h"
 
@@ -110,6 +111,35 @@ void run1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* pa
   if (dtype == 0) run1d<float, K>(p, x, y, packed);
   else if (dtype == 1) run1d<__nv_bfloat16, K>(p, x, y, packed);
   else run1d<__half, K>(p, x, y, packed);
+}
+
+// parameter-gradient kernels
+template <typename T>
+void run_pyramid_level(const PyramidLevel& a, const void* in, float* S) {
+  const long long total = (long long)a.B * a.Hs * a.Ws * a.C;
+  for (long long i = 0; i < total; ++i) pyramid_item<T>(a, static_cast<const T*>(in), S, i);
+}
+
+template <typename T, int K>
+void run_wgrad(const WGradSet& a, int nsub, const void* S, const void* G, float* stat, long long sub_s, long long sub_g,
+               long long sub_stat) {
+  AlignedBuf smem(kWgradWarps * (K * K + 1) * 32 + 16);
+  for (int sb = 0; sb < nsub; ++sb)
+    for (int split = 0; split < a.nsplit; ++split)
+      for (int cg = 0; cg < (a.C + 31) / 32; ++cg) {
+        for (int i = 0; i < kWgradWarps * (K * K + 1) * 32 + 16; ++i) smem.p[i] = 1.0e30f;
+        wgrad_cta<T, K>(a, static_cast<const T*>(S) + sb * sub_s, static_cast<const T*>(G) + sb * sub_g,
+                        stat + sb * sub_stat, smem.p, cg, split);
+      }
+}
+
+template <typename T>
+void run_wgrad_k(const WGradSet& a, int K, int nsub, const void* S, const void* G, float* stat, long long sub_s,
+                 long long sub_g, long long sub_stat) {
+  if (K == 1) run_wgrad<T, 1>(a, nsub, S, G, stat, sub_s, sub_g, sub_stat);
+  else if (K == 3) run_wgrad<T, 3>(a, nsub, S, G, stat, sub_s, sub_g, sub_stat);
+  else if (K == 5) run_wgrad<T, 5>(a, nsub, S, G, stat, sub_s, sub_g, sub_stat);
+  else run_wgrad<T, 7>(a, nsub, S, G, stat, sub_s, sub_g, sub_stat);
 }
 
 int ptr_align(const void* p) {
@@ -224,6 +254,56 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
       case 7: run2d_k<7>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
       default: return WTCONV_ERR_BAD_KERNEL_SIZE;
     }
+  }
+  return 0;
+}
+
+// Parameter-gradient kernels: pyramid of a tensor (levels concatenated, (B,H_l,W_l,4,C) each)
+int emu_wtconv2d_pyramid(const void* t, float* pyramid, int B, int C, int H, int W, int L, int dtype,
+                         const long long* strides) {
+  PyramidLevel a;
+  a.B = B; a.C = C;
+  int h = H, w = W;
+  const void* src = t;
+  int sdt = dtype;
+  long long in_s[4] = {strides[0], strides[1], strides[2], strides[3]};
+  float* out = pyramid;
+  for (int l = 0; l < L; ++l) {
+    a.Hin = h; a.Win = w; a.Hs = (h + 1) / 2; a.Ws = (w + 1) / 2;
+    for (int i = 0; i < 4; ++i) a.in_s[i] = in_s[i];
+    if (sdt == 0) run_pyramid_level<float>(a, src, out);
+    else if (sdt == 1) run_pyramid_level<__nv_bfloat16>(a, src, out);
+    else run_pyramid_level<__half>(a, src, out);
+    src = out; sdt = 0;
+    h = a.Hs; w = a.Ws;
+    in_s[0] = (long long)h * w * 4 * C; in_s[1] = 1; in_s[2] = (long long)w * 4 * C; in_s[3] = 4LL * C;
+    out += (size_t)B * h * w * 4 * C;
+  }
+  return 0;
+}
+
+// `nsplit` CTAs per channel group share the items, as on the device
+int emu_wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* xp, const float* gp, float* stats, int B,
+                                   int C, int H, int W, int K, int L, int dtype, const long long* xs,
+                                   const long long* gs, int nsplit) {
+  const int per_set = (K * K + 1) * C;
+  for (long long i = 0; i < (long long)(1 + 4 * L) * per_set; ++i) stats[i] = 0.f;
+  WGradSet a;
+  a.B = B; a.C = C; a.h = H; a.w = W;
+  a.tiles_y = cdiv(H, kWgradTH); a.tiles_x = cdiv(W, kWgradTW); a.nsplit = nsplit;
+  for (int i = 0; i < 4; ++i) { a.s_s[i] = xs[i]; a.g_s[i] = gs[i]; }
+  if (dtype == 0) run_wgrad_k<float>(a, K, 1, x, gy, stats, 0, 0, 0);
+  else if (dtype == 1) run_wgrad_k<__nv_bfloat16>(a, K, 1, x, gy, stats, 0, 0, 0);
+  else run_wgrad_k<__half>(a, K, 1, x, gy, stats, 0, 0, 0);
+  int h = H, w = W;
+  size_t off = 0;
+  for (int l = 0; l < L; ++l) {
+    h = (h + 1) / 2; w = (w + 1) / 2;
+    a.h = h; a.w = w; a.tiles_y = cdiv(h, kWgradTH); a.tiles_x = cdiv(w, kWgradTW);
+    const long long ps[4] = {(long long)h * w * 4 * C, 1, (long long)w * 4 * C, 4LL * C};
+    for (int i = 0; i < 4; ++i) { a.s_s[i] = ps[i]; a.g_s[i] = ps[i]; }
+    run_wgrad_k<float>(a, K, 4, xp + off, gp + off, stats + (size_t)(1 + 4 * l) * per_set, C, C, per_set);
+    off += (size_t)B * h * w * 4 * C;
   }
   return 0;
 }

@@ -44,7 +44,8 @@ def lib():
     global _lib
     if _lib is None:
         _lib = ctypes.CDLL(build())
-        for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force", "emu_regplane"):
+        for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force", "emu_regplane",
+                     "emu_wtconv2d_pyramid", "emu_wtconv2d_weight_grad_stats"):
             getattr(_lib, name).restype = ctypes.c_int
     return _lib
 
@@ -111,3 +112,24 @@ def forward1d(x, packed, K, L, stride=1, force=(0, 0, 0)):
     lib().emu_force(0, 0, 0, 0)
     assert st == 0, f"emulation status {st}"
     return y, list(info)
+
+
+def weight_grad_stats(x, gy, K, L, nsplit=2):
+    """Correlation sums of the parameter gradients (emulated kernels): tensor (1+4L, K*K+1, C)."""
+    B, C, H, W = x.shape
+    n = 0
+    h, w = H, W
+    for _ in range(L):
+        h, w = (h + 1) // 2, (w + 1) // 2
+        n += B * h * w * 4 * C
+    xp = torch.full((max(n, 1),), float("nan"), dtype=torch.float32)
+    gp = torch.full((max(n, 1),), float("nan"), dtype=torch.float32)
+    xs = (ctypes.c_longlong * 4)(*x.stride())
+    gs = (ctypes.c_longlong * 4)(*gy.stride())
+    code = DTYPE_CODE[x.dtype]
+    assert lib().emu_wtconv2d_pyramid(_ptr(x), _ptr(xp), B, C, H, W, L, code, xs) == 0
+    assert lib().emu_wtconv2d_pyramid(_ptr(gy), _ptr(gp), B, C, H, W, L, code, gs) == 0
+    stats = torch.full((1 + 4 * L, K * K + 1, C), float("nan"), dtype=torch.float32)
+    assert lib().emu_wtconv2d_weight_grad_stats(_ptr(x), _ptr(gy), _ptr(xp), _ptr(gp), _ptr(stats), B, C, H, W, K, L,
+                                                code, xs, gs, nsplit) == 0
+    return stats

@@ -111,3 +111,41 @@ def test_emulated_input_gradient(ndim, shape, L, K):
     else:
         out, _ = emu_lib.forward1d(g32, packed, K, L)
     assert max_err(out.double().numpy(), gx.numpy()) <= 1e-5
+
+
+# Parameter gradients: pyramid + correlation-sum kernels (emulated) and the per-parameter scaling of
+# wtconv_b200.modules.param_grads_from_stats against autograd through the oracle.
+@pytest.mark.parametrize("shape,L,K,bias,layout", [((2, 5, 14, 13), 3, 5, True, "cl"), ((1, 4, 30, 17), 2, 3, False, "nchw"),
+                                                    ((2, 33, 7, 7), 2, 5, True, "cl"), ((1, 3, 9, 20), 4, 7, True, "nchw")])
+def test_emulated_parameter_gradients(shape, L, K, bias, layout):
+    from oracle import wtconv_torch
+    from wtconv_b200.modules import param_grads_from_stats
+    torch.manual_seed(sum(shape) + K)
+    C = shape[1]
+    params = wtconv_torch.random_params(C, K, L, ndim=2, bias=bias)
+    for i in range(L):
+        params[f"wavelet_scale.{i}.weight"].uniform_(0.05, 0.3)
+    params["base_scale.weight"].uniform_(0.5, 1.5)
+    pd = {k: v.double().requires_grad_(True) for k, v in params.items()}
+    x = torch.randn(shape)
+    y = wtconv_torch.wtconv2d_forward(x.double(), pd)
+    gy = torch.randn(y.shape)
+    names = ["base_conv.weight", "base_conv.bias", "base_scale.weight"]
+    for i in range(L):
+        names += [f"wavelet_convs.{i}.weight", f"wavelet_scale.{i}.weight"]
+    have = [n for n in names if n in pd]
+    ref = dict(zip(have, torch.autograd.grad(y, [pd[n] for n in have], gy.double())))
+    xt, gt = x, gy
+    if layout == "cl":
+        xt = xt.contiguous(memory_format=torch.channels_last)
+        gt = gt.contiguous(memory_format=torch.channels_last)
+    stats = emu_lib.weight_grad_stats(xt, gt, K, L)
+    assert not torch.isnan(stats).any()
+    ana, syn = emu_lib.taps(2, torch.float32)
+    grads = param_grads_from_stats(stats, [params.get(n) for n in names], ana * syn)
+    for n, gr in zip(names, grads):
+        if n not in ref:
+            assert gr is None
+            continue
+        err = float((gr.double() - ref[n]).abs().max() / ref[n].abs().max())
+        assert err <= 1e-5, f"{n}: {err:.3e}"

@@ -368,9 +368,9 @@ def test_c_abi_error_codes():
     m = wtconv_b200.WTConv2d(4, 4, kernel_size=9, wt_levels=1).to(dev)
     with torch.no_grad(), pytest.raises(ValueError):
         m(x)
-    m = wtconv_b200.WTConv2d(4, 4, kernel_size=5, wt_levels=1).to(dev)
+    m1 = wtconv_b200.WTConv1d(4, 4, kernel_size=5, wt_levels=1).to(dev)
     with pytest.raises(NotImplementedError):
-        m(x)                                     # grad mode with trainable parameters: not implemented
+        m1(x[:, :, 0])                           # 1-D, grad mode with trainable parameters: not implemented
     torch.cuda.synchronize()
 
 
@@ -406,3 +406,41 @@ def test_input_gradient(ndim, shape, L, K, stride, layout, dtype):
     assert tuple(gx.shape) == tuple(x.shape)
     assert max_err(y.detach().float().cpu().numpy(), yr.detach().numpy()) <= TOL[dtype]
     assert max_err(gx.float().cpu().numpy(), gr.numpy()) <= TOL[dtype]
+
+
+# Full backward of the 2-D layer (input and every parameter) against autograd through the oracle.
+@pytest.mark.parametrize("shape,L,K,stride,bias,layout,dtype", [
+    ((4, 24, 56, 56), 5, 5, 1, True, "cl", torch.float32), ((3, 40, 14, 13), 3, 5, 1, True, "cl", torch.float32),
+    ((2, 6, 21, 30), 3, 3, 1, False, "nchw", torch.float32), ((2, 4, 17, 16), 2, 5, 2, True, "nchw", torch.float32),
+    ((8, 64, 7, 7), 2, 5, 1, True, "cl", torch.bfloat16), ((1, 4, 90, 50), 4, 7, 1, True, "cl", torch.float32),
+])
+def test_parameter_gradients(shape, L, K, stride, bias, layout, dtype):
+    dev = _cuda()
+    C = shape[1]
+    params = wtconv_torch.random_params(C, K, L, ndim=2, bias=bias, seed=sum(shape))
+    g = torch.Generator().manual_seed(shape[-1])
+    for i in range(L):
+        params[f"wavelet_scale.{i}.weight"] = torch.empty_like(torch.as_tensor(params[f"wavelet_scale.{i}.weight"])).uniform_(0.05, 0.3, generator=g)
+    x = torch.randn(shape, generator=g)
+    m = _module(2, C, K, L, stride, bias, params, dtype, dev).train()
+    xt = x.to(dev).to(dtype)
+    if layout == "cl":
+        xt = xt.contiguous(memory_format=torch.channels_last)
+    xt.requires_grad_(True)
+    y = m(xt)
+    gy = torch.randn(y.shape, generator=g)
+    y.backward(gy.to(dev).to(dtype))
+    # oracle in fp64 on the parameter values the module holds
+    names = [n for n, _ in m.named_parameters() if "filter" not in n]
+    pd = {n: p.detach().cpu().double().requires_grad_(True) for n, p in m.named_parameters() if "filter" not in n}
+    xr = x.to(dtype).double().requires_grad_(True)
+    yr = wtconv_torch.wtconv2d_forward(xr, pd, stride=stride)
+    refs = torch.autograd.grad(yr, [xr] + [pd[n] for n in names], gy.to(dtype).double())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2      # sums over B*H*W terms in fp32 / results rounded to bf16
+    assert max_err(xt.grad.float().cpu().numpy(), refs[0].numpy()) <= TOL[dtype]
+    got = dict(m.named_parameters())
+    for n, r in zip(names, refs[1:]):
+        assert got[n].grad is not None, n
+        err = max_err(got[n].grad.float().cpu().numpy(), r.numpy())
+        assert err <= tol, f"{n}: {err:.3e}"
+    assert m.wt_filter.grad is None and m.iwt_filter.grad is None

@@ -29,6 +29,10 @@ SYMBOLS = {
                                 ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),
     "wtconv_pack_params_adjoint": (_I, [_I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _VP, _VP, _VP,
                                         ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),
+    "wtconv2d_pyramid_floats": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
+    "wtconv2d_pyramid": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _LLP, _VP]),
+    "wtconv2d_weight_grad_stat_floats": (ctypes.c_size_t, [_I, _I, _I]),
+    "wtconv2d_weight_grad_stats": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, _VP]),
     "wtconv2d_workspace_bytes": (_I, [_I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, ctypes.POINTER(ctypes.c_size_t)]),
     "wtconv2d_launch_count": (_I, [_I, _I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, ctypes.POINTER(_I)]),
     "wtconv2d_forward": (_I, [_VP, _VP, _VP, _VP, ctypes.c_size_t, _I, _I, _I, _I, _I, _I, _I, _I, _LLP, _LLP, _VP]),

@@ -10,6 +10,7 @@
 #include "../../include/wtconv_b200.h"
 #include "wt1d_host.h"
 #include "wt2d_host.h"
+#include "wt2d_wgrad.cuh"
 #include "wt_aux.h"
 
 using namespace wt;
@@ -196,6 +197,94 @@ int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype, d
                                void* stream) {
   return pack_params_impl(1, ndim, C, K, L, param_dtype, ana_tap, syn_tap, base_w, base_b, base_scale, wavelet_w,
                           wavelet_scale, packed, stream);
+}
+
+size_t wtconv2d_pyramid_floats(int B, int C, int H, int W, int L) {
+  if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || L < 0 || L > kMaxLevels) return 0;
+  size_t total = 0;
+  int h = H, w = W;
+  for (int l = 0; l < L; ++l) {
+    h = (h + 1) / 2; w = (w + 1) / 2;
+    total += (size_t)B * h * w * 4 * C;
+  }
+  return total;
+}
+
+int wtconv2d_pyramid(const void* t, float* pyramid, int B, int C, int H, int W, int L, int dtype,
+                     const long long* strides, void* stream) {
+  if (!t || (!pyramid && L > 0)) return WTCONV_ERR_BAD_ARG;
+  if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || !valid_dtype(dtype)) return WTCONV_ERR_BAD_ARG;
+  if (L < 0 || L > kMaxLevels) return WTCONV_ERR_BAD_LEVELS;
+  if ((long long)B * C * H * W >= (1LL << 40)) return WTCONV_ERR_TOO_LARGE;
+  const long long dflt[4] = {(long long)C * H * W, (long long)H * W, W, 1};
+  PyramidLevel a;
+  a.B = B; a.C = C;
+  int h = H, w = W;
+  const void* src = t;
+  int src_dtype = dtype;
+  long long in_s[4];
+  for (int i = 0; i < 4; ++i) in_s[i] = strides ? strides[i] : dflt[i];
+  float* out = pyramid;
+  for (int l = 0; l < L; ++l) {
+    a.Hin = h; a.Win = w;
+    a.Hs = (h + 1) / 2; a.Ws = (w + 1) / 2;
+    for (int i = 0; i < 4; ++i) a.in_s[i] = in_s[i];
+    const cudaError_t e = launch_pyramid_level(a, src_dtype, src, out, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return (int)e;
+    // the next level reads the low-pass sub-band just written: (B, Hs, Ws, 4, C), sub-band 0
+    src = out; src_dtype = WTCONV_F32;
+    h = a.Hs; w = a.Ws;
+    in_s[0] = (long long)h * w * 4 * C; in_s[1] = 1; in_s[2] = (long long)w * 4 * C; in_s[3] = 4LL * C;
+    out += (size_t)B * h * w * 4 * C;
+  }
+  return WTCONV_OK;
+}
+
+size_t wtconv2d_weight_grad_stat_floats(int C, int K, int L) {
+  if (C <= 0 || K < 1 || L < 0) return 0;
+  return (size_t)(1 + 4 * L) * (K * K + 1) * C;
+}
+
+int wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x_pyramid, const float* g_pyramid,
+                               float* stats, int B, int C, int H, int W, int K, int L, int dtype,
+                               const long long* x_strides, const long long* g_strides, void* stream) {
+  if (!x || !gy || !stats || (L > 0 && (!x_pyramid || !g_pyramid))) return WTCONV_ERR_BAD_ARG;
+  const int st = check_common(C, K, L, dtype);
+  if (st) return st;
+  if (B <= 0 || H <= 0 || W <= 0) return WTCONV_ERR_BAD_ARG;
+  if ((long long)B * C * H * W >= (1LL << 40) || (long long)C * H * W >= (1LL << 31)) return WTCONV_ERR_TOO_LARGE;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const size_t nstat = wtconv2d_weight_grad_stat_floats(C, K, L);
+  cudaError_t e = cudaMemsetAsync(stats, 0, nstat * sizeof(float), cs);
+  if (e != cudaSuccess) return (int)e;
+  const long long dflt[4] = {(long long)C * H * W, (long long)H * W, W, 1};
+  const int per_set = (K * K + 1) * C;
+  auto geometry = [&](WGradSet& a, int h, int w, int nsub) {
+    a.B = B; a.C = C; a.h = h; a.w = w;
+    a.tiles_y = cdiv(h, kWgradTH); a.tiles_x = cdiv(w, kWgradTW);
+    const long long items = (long long)B * a.tiles_y * a.tiles_x;
+    const long long want = cdiv(888, imax(1, cdiv(C, 32) * nsub));            // about two waves of CTAs
+    const long long most = (items + kWgradWarps - 1) / kWgradWarps;
+    a.nsplit = (int)imax(1, (int)(want < most ? want : most));
+  };
+  WGradSet a;
+  geometry(a, H, W, 1);
+  for (int i = 0; i < 4; ++i) { a.s_s[i] = x_strides ? x_strides[i] : dflt[i]; a.g_s[i] = g_strides ? g_strides[i] : dflt[i]; }
+  e = launch_wgrad(a, K, dtype, 1, x, gy, stats, 0, 0, 0, cs);
+  if (e != cudaSuccess) return (int)e;
+  int h = H, w = W;
+  size_t off = 0;
+  for (int l = 0; l < L; ++l) {
+    h = (h + 1) / 2; w = (w + 1) / 2;
+    geometry(a, h, w, 4);
+    const long long ps[4] = {(long long)h * w * 4 * C, 1, (long long)w * 4 * C, 4LL * C};
+    for (int i = 0; i < 4; ++i) { a.s_s[i] = ps[i]; a.g_s[i] = ps[i]; }
+    e = launch_wgrad(a, K, WTCONV_F32, 4, x_pyramid + off, g_pyramid + off, stats + (size_t)(1 + 4 * l) * per_set, C, C,
+                     per_set, cs);
+    if (e != cudaSuccess) return (int)e;
+    off += (size_t)B * h * w * 4 * C;
+  }
+  return WTCONV_OK;
 }
 
 int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, const long long* x_strides,

@@ -13,6 +13,8 @@ struct Plan2d;
 struct Plan1d;
 struct RegPlane;
 struct QuadPlane;
+struct PyramidLevel;
+struct WGradSet;
 
 struct PackArgs {
   int C, L, taps, tapset, subbands;
@@ -111,6 +113,11 @@ cudaError_t launch_regplane(const RegPlane& a, int dtype, const void* x, void* y
 
 cudaError_t launch_quad(const QuadPlane& a, int dtype, const void* x, void* y, const float* rin, float* rout,
                         const float* packed, size_t smem_bytes, cudaStream_t stream);
+
+cudaError_t launch_pyramid_level(const PyramidLevel& a, int dtype, const void* in, float* S, cudaStream_t stream);
+
+cudaError_t launch_wgrad(const WGradSet& a, int K, int dtype, int nsub, const void* S, const void* G, float* stat,
+                         long long sub_s, long long sub_g, long long sub_stat, cudaStream_t stream);
 
 template <int K>
 cudaError_t launch_wt1d_k(const Plan1d& p, int dtype, const void* x, void* y, const float* packed,
