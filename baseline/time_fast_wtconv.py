@@ -59,6 +59,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--install", metavar="CHECKOUT", help="copy and build the reference backend, then exit")
     ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--backward", action="store_true", help="time forward + backward (input and parameter gradients)")
     args = ap.parse_args()
     if args.install:
         return install(args.install)
@@ -81,8 +82,23 @@ def main():
                     ref.wt_scales[i].copy_(sd[f"wavelet_scale.{i}.weight"])
                 x = torch.randn(args.batch, C, H, H, device=dev, dtype=dtype)
                 xcl = x.contiguous(memory_format=torch.channels_last)
-                ms_ref, yr = event_ms(lambda: ref(x))
-                ms_ours, yo = event_ms(lambda: ours(xcl))
+                if not args.backward:
+                    ms_ref, yr = event_ms(lambda: ref(x))
+                    ms_ours, yo = event_ms(lambda: ours(xcl))
+            if args.backward:
+                gy = torch.randn_like(x)
+                gycl = gy.contiguous(memory_format=torch.channels_last)
+                xr, xo = x.clone().requires_grad_(True), xcl.clone().requires_grad_(True)
+
+                def step(m, xin, g):
+                    m.zero_grad(set_to_none=True)
+                    xin.grad = None
+                    y = m(xin)
+                    y.backward(g)
+                    return xin.grad
+
+                ms_ref, yr = event_ms(lambda: step(ref, xr, gy))
+                ms_ours, yo = event_ms(lambda: step(ours, xo, gycl))
             diff = float((yo.float() - yr.float()).abs().max() / yr.float().abs().max())
             print(f"{str(dtype)[6:]:9s} C={C:4d} H={H:3d} L={L}: fast_wtconv CUDA (NCHW) {ms_ref * 1e3:8.1f} us | "
                   f"this library (channels-last) {ms_ours * 1e3:8.1f} us | ratio {ms_ref / ms_ours:5.2f} | "
