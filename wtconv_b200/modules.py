@@ -7,8 +7,11 @@ same sub-module / parameter names and shapes (so ``state_dict`` round-trips with
 same seeded initialisation stream.  They plug into the reference model zoo
 through its ``wtconv_class=`` hook (``wtconvnext/wtconvnext.py:76,105-114``).
 
-Only the forward pass exists, and only on CUDA: the whole cascade runs in the
-fused kernels of ``libwtconv_b200.so``; there is no PyTorch-op or CPU path.
+Everything runs on CUDA only, in the kernels of ``libwtconv_b200.so``: there is no
+PyTorch-op or CPU path.  ``WTConv2d`` is one autograd node (input gradient: the forward
+kernels on the adjoint parameter block; parameter gradients: correlation sums between
+sub-band pyramids, scaled per parameter here with a few tiny tensor operations);
+``WTConv1d`` is differentiable with respect to its input only.
 """
 from __future__ import annotations
 
