@@ -128,9 +128,23 @@ int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype,
  *   d wavelet_convs[l].weight[4c+s] = wavelet_scale[l][4c+s] * g_l * stats[1+4l+s],
  *   d wavelet_scale[l][4c+s] = g_l * <wavelet_convs[l].weight[4c+s], stats[1+4l+s]>,
  * with g_l = (ana_tap * syn_tap)^(l+1).  Sums are accumulated with floating-point
- * atomics (order not fixed, like the reference's kernels).
+ * atomics (order not fixed, like the reference's kernels).  A 1-D layer
+ * (wtconv/wtconv1d.py:46-85) passes its signal as a one-row image (H = 1, row
+ * stride 0): its low / high band are sub-bands 0 and 2, its K taps the middle row
+ * of the K x K sums.
  */
 size_t wtconv2d_pyramid_floats(int B, int C, int H, int W, int L);
+/*
+ * wtconv_param_grads applies those factors: one small launch writes the gradient
+ * of every parameter (contiguous buffers of the parameter dtype and shape;
+ * pointer arguments as for wtconv_pack_params, g_* the gradients) from `stats`.
+ * ndim = 1 reads the one-row-image sums as described below.
+ */
+int wtconv_param_grads(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                       const float* stats, const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale, void* g_base_w,
+                       void* g_base_b, void* g_base_scale, void* const* g_wavelet_w, void* const* g_wavelet_scale,
+                       void* stream);
 int wtconv2d_pyramid(const void* t, float* pyramid, int B, int C, int H, int W, int L, int dtype,
                      const long long* strides, void* stream);
 size_t wtconv2d_weight_grad_stat_floats(int C, int K, int L);

@@ -308,6 +308,26 @@ int emu_wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x
   return 0;
 }
 
+int emu_param_grads(int ndim, int C, int K, int L, double ana_tap, double syn_tap, const float* stats,
+                    const void* base_w, const void* base_b, const void* base_scale, const void* const* wavelet_w,
+                    const void* const* wavelet_scale, void* g_base_w, void* g_base_b, void* g_base_scale,
+                    void* const* g_wavelet_w, void* const* g_wavelet_scale) {
+  GradArgs a;
+  a.ndim = ndim; a.C = C; a.K = K; a.L = L; a.stats = stats;
+  a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  a.g_base_w = g_base_w; a.g_base_b = g_base_b; a.g_base_scale = g_base_scale;
+  double g = 1.0;
+  for (int l = 0; l < L; ++l) {
+    a.wavelet_w[l] = wavelet_w[l]; a.wavelet_scale[l] = wavelet_scale[l];
+    a.g_wavelet_w[l] = g_wavelet_w[l]; a.g_wavelet_scale[l] = g_wavelet_scale[l];
+    g *= ana_tap * syn_tap;
+    a.gain[l] = g;
+  }
+  const int nsub = ndim == 2 ? 4 : 2;
+  for (long long i = 0; i < (long long)(1 + nsub * L) * C; ++i) param_grad_item<float>(a, i);
+  return 0;
+}
+
 int emu_wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, int N, int K, int L, int stride,
                          int dtype, const long long* xs, const long long* ys, int* info) {
   Layer1d ly;

@@ -45,7 +45,7 @@ def lib():
     if _lib is None:
         _lib = ctypes.CDLL(build())
         for name in ("emu_pack_params", "emu_wtconv2d_forward", "emu_wtconv1d_forward", "emu_force", "emu_regplane",
-                     "emu_wtconv2d_pyramid", "emu_wtconv2d_weight_grad_stats"):
+                     "emu_wtconv2d_pyramid", "emu_wtconv2d_weight_grad_stats", "emu_param_grads"):
             getattr(_lib, name).restype = ctypes.c_int
     return _lib
 
@@ -133,3 +133,17 @@ def weight_grad_stats(x, gy, K, L, nsplit=2):
     assert lib().emu_wtconv2d_weight_grad_stats(_ptr(x), _ptr(gy), _ptr(xp), _ptr(gp), _ptr(stats), B, C, H, W, K, L,
                                                 code, xs, gs, nsplit) == 0
     return stats
+
+
+def param_grads(stats, params, names, ndim, C, K, L):
+    """Parameter gradients from the correlation sums (emulated wtconv_param_grads, fp32 parameters)."""
+    p = [params[n].float().contiguous() if n in params else None for n in names]
+    g = [torch.full_like(t, float("nan")) if t is not None else None for t in p]
+    arr_t = ctypes.c_void_p * max(L, 1)
+    ptrs = lambda ts, first: arr_t(*[ts[first + 2 * i].data_ptr() for i in range(L)])
+    ana, syn = taps(ndim, torch.float32)
+    st = lib().emu_param_grads(ndim, C, K, L, ctypes.c_double(ana), ctypes.c_double(syn), _ptr(stats),
+                               _ptr(p[0]), _ptr(p[1]), _ptr(p[2]), ptrs(p, 3), ptrs(p, 4),
+                               _ptr(g[0]), _ptr(g[1]), _ptr(g[2]), ptrs(g, 3), ptrs(g, 4))
+    assert st == 0
+    return g

@@ -113,13 +113,12 @@ def test_emulated_input_gradient(ndim, shape, L, K):
     assert max_err(out.double().numpy(), gx.numpy()) <= 1e-5
 
 
-# Parameter gradients: pyramid + correlation-sum kernels (emulated) and the per-parameter scaling of
-# wtconv_b200.modules.param_grads_from_stats against autograd through the oracle.
+# Parameter gradients: pyramid, correlation-sum and per-parameter scaling kernels (emulated) against
+# autograd through the oracle.
 @pytest.mark.parametrize("shape,L,K,bias,layout", [((2, 5, 14, 13), 3, 5, True, "cl"), ((1, 4, 30, 17), 2, 3, False, "nchw"),
                                                     ((2, 33, 7, 7), 2, 5, True, "cl"), ((1, 3, 9, 20), 4, 7, True, "nchw")])
 def test_emulated_parameter_gradients(shape, L, K, bias, layout):
     from oracle import wtconv_torch
-    from wtconv_b200.modules import param_grads_from_stats
     torch.manual_seed(sum(shape) + K)
     C = shape[1]
     params = wtconv_torch.random_params(C, K, L, ndim=2, bias=bias)
@@ -141,11 +140,32 @@ def test_emulated_parameter_gradients(shape, L, K, bias, layout):
         gt = gt.contiguous(memory_format=torch.channels_last)
     stats = emu_lib.weight_grad_stats(xt, gt, K, L)
     assert not torch.isnan(stats).any()
-    ana, syn = emu_lib.taps(2, torch.float32)
-    grads = param_grads_from_stats(stats, [params.get(n) for n in names], ana * syn)
+    grads = emu_lib.param_grads(stats, params, names, 2, C, K, L)
     for n, gr in zip(names, grads):
         if n not in ref:
             assert gr is None
             continue
         err = float((gr.double() - ref[n]).abs().max() / ref[n].abs().max())
+        assert err <= 1e-5, f"{n}: {err:.3e}"
+
+
+def test_emulated_parameter_gradients_1d():
+    """1-D layers reuse the 2-D kernels on the signal viewed as a one-row image."""
+    from oracle import wtconv_torch
+    torch.manual_seed(5)
+    C, K, L = 6, 5, 3
+    params = wtconv_torch.random_params(C, K, L, ndim=1, bias=True)
+    pd = {k: v.double().requires_grad_(True) for k, v in params.items()}
+    x = torch.randn(2, C, 133)
+    y = wtconv_torch.wtconv1d_forward(x.double(), pd)
+    gy = torch.randn(y.shape)
+    names = ["base_conv.weight", "base_conv.bias", "base_scale.weight"]
+    for i in range(L):
+        names += [f"wavelet_convs.{i}.weight", f"wavelet_scale.{i}.weight"]
+    ref = torch.autograd.grad(y, [pd[n] for n in names], gy.double())
+    stats = emu_lib.weight_grad_stats(x.unsqueeze(2), gy.unsqueeze(2), K, L)
+    grads = emu_lib.param_grads(stats, params, names, 1, C, K, L)
+    for n, gr, r in zip(names, grads, ref):
+        assert tuple(gr.shape) == tuple(r.shape), n
+        err = float((gr.double() - r).abs().max() / r.abs().max())
         assert err <= 1e-5, f"{n}: {err:.3e}"

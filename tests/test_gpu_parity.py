@@ -368,9 +368,6 @@ def test_c_abi_error_codes():
     m = wtconv_b200.WTConv2d(4, 4, kernel_size=9, wt_levels=1).to(dev)
     with torch.no_grad(), pytest.raises(ValueError):
         m(x)
-    m1 = wtconv_b200.WTConv1d(4, 4, kernel_size=5, wt_levels=1).to(dev)
-    with pytest.raises(NotImplementedError):
-        m1(x[:, :, 0])                           # 1-D, grad mode with trainable parameters: not implemented
     torch.cuda.synchronize()
 
 
@@ -444,3 +441,27 @@ def test_parameter_gradients(shape, L, K, stride, bias, layout, dtype):
         err = max_err(got[n].grad.float().cpu().numpy(), r.numpy())
         assert err <= tol, f"{n}: {err:.3e}"
     assert m.wt_filter.grad is None and m.iwt_filter.grad is None
+
+
+@pytest.mark.parametrize("shape,L,K,stride", [((3, 8, 515), 4, 5, 1), ((2, 4, 100), 3, 3, 2), ((4, 64, 4096), 4, 5, 1)])
+def test_parameter_gradients_1d(shape, L, K, stride):
+    dev = _cuda()
+    C = shape[1]
+    params = wtconv_torch.random_params(C, K, L, ndim=1, bias=True, seed=sum(shape))
+    g = torch.Generator().manual_seed(shape[-1])
+    x = torch.randn(shape, generator=g)
+    m = _module(1, C, K, L, stride, True, params, torch.float32, dev).train()
+    xt = x.to(dev).requires_grad_(True)
+    y = m(xt)
+    gy = torch.randn(y.shape, generator=g)
+    y.backward(gy.to(dev))
+    names = [n for n, _ in m.named_parameters() if "filter" not in n]
+    pd = {n: p.detach().cpu().double().requires_grad_(True) for n, p in m.named_parameters() if "filter" not in n}
+    xr = x.double().requires_grad_(True)
+    yr = wtconv_torch.wtconv1d_forward(xr, pd, stride=stride)
+    refs = torch.autograd.grad(yr, [xr] + [pd[n] for n in names], gy.double())
+    assert max_err(xt.grad.cpu().numpy(), refs[0].numpy()) <= 1e-5
+    got = dict(m.named_parameters())
+    for n, r in zip(names, refs[1:]):
+        err = max_err(got[n].grad.cpu().numpy(), r.numpy())
+        assert err <= 1e-4, f"{n}: {err:.3e}"

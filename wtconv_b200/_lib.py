@@ -29,6 +29,9 @@ SYMBOLS = {
                                 ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),
     "wtconv_pack_params_adjoint": (_I, [_I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _VP, _VP, _VP,
                                         ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),
+    "wtconv_param_grads": (_I, [_I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _VP, _VP, _VP, _VP,
+                                ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP, _VP, ctypes.POINTER(_VP),
+                                ctypes.POINTER(_VP), _VP]),
     "wtconv2d_pyramid_floats": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "wtconv2d_pyramid": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _LLP, _VP]),
     "wtconv2d_weight_grad_stat_floats": (ctypes.c_size_t, [_I, _I, _I]),

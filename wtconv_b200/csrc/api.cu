@@ -287,6 +287,37 @@ int wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x_pyr
   return WTCONV_OK;
 }
 
+int wtconv_param_grads(int ndim, int C, int K, int L, int param_dtype, double ana_tap, double syn_tap,
+                       const float* stats, const void* base_w, const void* base_b, const void* base_scale,
+                       const void* const* wavelet_w, const void* const* wavelet_scale, void* g_base_w,
+                       void* g_base_b, void* g_base_scale, void* const* g_wavelet_w, void* const* g_wavelet_scale,
+                       void* stream) {
+  if (ndim != 1 && ndim != 2) return WTCONV_ERR_BAD_ARG;
+  const int st = check_common(C, K, L, param_dtype);
+  if (st) return st;
+  if (!stats || !base_w || !base_scale || !g_base_w || !g_base_scale || (base_b && !g_base_b) ||
+      (L > 0 && (!wavelet_w || !wavelet_scale || !g_wavelet_w || !g_wavelet_scale)))
+    return WTCONV_ERR_BAD_ARG;
+  GradArgs a;
+  a.ndim = ndim; a.C = C; a.K = K; a.L = L;
+  a.stats = stats;
+  a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  a.g_base_w = g_base_w; a.g_base_b = g_base_b; a.g_base_scale = g_base_scale;
+  double g = 1.0;
+  for (int l = 0; l < kMaxLevels; ++l) {
+    a.wavelet_w[l] = nullptr; a.wavelet_scale[l] = nullptr; a.g_wavelet_w[l] = nullptr; a.g_wavelet_scale[l] = nullptr;
+    a.gain[l] = 0.0;
+  }
+  for (int l = 0; l < L; ++l) {
+    if (!wavelet_w[l] || !wavelet_scale[l] || !g_wavelet_w[l] || !g_wavelet_scale[l]) return WTCONV_ERR_BAD_ARG;
+    a.wavelet_w[l] = wavelet_w[l]; a.wavelet_scale[l] = wavelet_scale[l];
+    a.g_wavelet_w[l] = g_wavelet_w[l]; a.g_wavelet_scale[l] = g_wavelet_scale[l];
+    g *= ana_tap * syn_tap;
+    a.gain[l] = g;
+  }
+  return (int)launch_param_grads(a, param_dtype, static_cast<cudaStream_t>(stream));
+}
+
 int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, const long long* x_strides,
                              const long long* y_strides, size_t* bytes) {
   if (!bytes) return WTCONV_ERR_BAD_ARG;

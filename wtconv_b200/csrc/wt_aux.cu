@@ -25,6 +25,28 @@ cudaError_t launch_pack(const PackArgs& a, int param_dtype, float* packed, cudaS
   return cudaGetLastError();
 }
 
+template <typename P>
+__global__ void param_grads_kernel(GradArgs a) {
+  const int nsub = (a.ndim == 2) ? 4 : 2;
+  const long long total = (long long)(1 + nsub * a.L) * a.C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x)
+    param_grad_item<P>(a, i);
+}
+
+cudaError_t launch_param_grads(const GradArgs& a, int param_dtype, cudaStream_t stream) {
+  const int nsub = (a.ndim == 2) ? 4 : 2;
+  const long long total = (long long)(1 + nsub * a.L) * a.C;
+  const int threads = 128;
+  const int blocks = (int)((total + threads - 1) / threads);
+  switch (param_dtype) {
+    case 0: param_grads_kernel<float><<<blocks, threads, 0, stream>>>(a); break;
+    case 1: param_grads_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(a); break;
+    default: param_grads_kernel<__half><<<blocks, threads, 0, stream>>>(a); break;
+  }
+  return cudaGetLastError();
+}
+
 template <typename T>
 __global__ void reduce_planes_kernel(const T* __restrict__ in, float* __restrict__ out, int B, int C, int Hin,
                                      int Win, int Hout, int Wout, int shift, long long s0, long long s1,

@@ -58,6 +58,72 @@ WT_HD float pack_value(const PackArgs& a, long long i) {
   return v;
 }
 
+// Parameter gradients from the correlation sums (see wt2d_wgrad.cuh): one item per
+// (output set, channel).  Output set 0 is the base path, 1 + S*l + s sub-band s of level l
+// (S = 4 in 2-D, 2 in 1-D).  1-D layers were summed as one-row images: their band s lives in
+// 2-D set 1 + 4l + 2s and their K taps in the middle row of the K x K sums.
+struct GradArgs {
+  int ndim, C, K, L;
+  const float* stats;            // (1+4L, K*K+1, C)
+  const void* base_w;
+  const void* base_b;            // may be null
+  const void* base_scale;
+  const void* wavelet_w[kMaxLevels];
+  const void* wavelet_scale[kMaxLevels];
+  void* g_base_w;
+  void* g_base_b;
+  void* g_base_scale;
+  void* g_wavelet_w[kMaxLevels];
+  void* g_wavelet_scale[kMaxLevels];
+  double gain[kMaxLevels];       // (analysis tap * synthesis tap)^(level+1)
+};
+
+template <typename P>
+WT_HD void param_grad_item(const GradArgs& a, long long idx) {
+  const int nsub = (a.ndim == 2) ? 4 : 2;
+  const int taps = (a.ndim == 2) ? a.K * a.K : a.K;
+  const int kk1 = a.K * a.K + 1;
+  const int c = (int)(idx % a.C);
+  const int oset = (int)(idx / a.C);
+  const int tap0 = (a.ndim == 2) ? 0 : (a.K / 2) * a.K;            // first of the taps in the K x K sums
+  if (oset == 0) {
+    const float* st = a.stats + c;
+    const float sc = Elem<P>::to_f(static_cast<const P*>(a.base_scale)[c]);
+    const P* w = static_cast<const P*>(a.base_w) + (size_t)c * taps;
+    P* gw = static_cast<P*>(a.g_base_w) + (size_t)c * taps;
+    float dot = 0.f;
+    for (int t = 0; t < taps; ++t) {
+      const float corr = st[(size_t)(tap0 + t) * a.C];
+      gw[t] = Elem<P>::from_f(sc * corr);
+      dot = fmaf(Elem<P>::to_f(w[t]), corr, dot);
+    }
+    const float sum_g = st[(size_t)(a.K * a.K) * a.C];
+    if (a.base_b) {
+      static_cast<P*>(a.g_base_b)[c] = Elem<P>::from_f(sc * sum_g);
+      dot = fmaf(Elem<P>::to_f(static_cast<const P*>(a.base_b)[c]), sum_g, dot);
+    }
+    static_cast<P*>(a.g_base_scale)[c] = Elem<P>::from_f(dot);
+  } else {
+    const int l = (oset - 1) / nsub, s = (oset - 1) - l * nsub;
+    const int set2d = 1 + 4 * l + ((a.ndim == 2) ? s : 2 * s);
+    const float* st = a.stats + (size_t)set2d * kk1 * a.C + c;
+    const int oc = nsub * c + s;
+    const float g = (float)a.gain[l];
+    const float sc = Elem<P>::to_f(static_cast<const P*>(a.wavelet_scale[l])[oc]);
+    const P* w = static_cast<const P*>(a.wavelet_w[l]) + (size_t)oc * taps;
+    P* gw = static_cast<P*>(a.g_wavelet_w[l]) + (size_t)oc * taps;
+    float dot = 0.f;
+    for (int t = 0; t < taps; ++t) {
+      const float corr = st[(size_t)(tap0 + t) * a.C];
+      gw[t] = Elem<P>::from_f(sc * g * corr);
+      dot = fmaf(Elem<P>::to_f(w[t]), corr, dot);
+    }
+    static_cast<P*>(a.g_wavelet_scale[l])[oc] = Elem<P>::from_f(g * dot);
+  }
+}
+
+cudaError_t launch_param_grads(const GradArgs& a, int param_dtype, cudaStream_t stream);
+
 // out[n][c][yo][xo] = sum of the 2^shift x 2^shift block of `in`, zero outside the
 // plane: the un-normalised low-pass plane `shift` levels further down
 // (wtconv/wtconv2d.py:49-54 applied `shift` times, taps folded into the parameters).

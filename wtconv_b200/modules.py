@@ -10,8 +10,8 @@ through its ``wtconv_class=`` hook (``wtconvnext/wtconvnext.py:76,105-114``).
 Everything runs on CUDA only, in the kernels of ``libwtconv_b200.so``: there is no
 PyTorch-op or CPU path.  ``WTConv2d`` is one autograd node (input gradient: the forward
 kernels on the adjoint parameter block; parameter gradients: correlation sums between
-sub-band pyramids, scaled per parameter here with a few tiny tensor operations);
-``WTConv1d`` is differentiable with respect to its input only.
+sub-band pyramids, scaled per parameter by one more small kernel);
+``WTConv1d`` uses the same kernels on the signal viewed as a one-row image.
 """
 from __future__ import annotations
 
@@ -167,14 +167,55 @@ class _WTConvNd(nn.Module):
         if torch.is_grad_enabled():
             ps = self._kernel_params()
             trainable = any(p is not None and p.requires_grad for p in ps)
-            if trainable and self._ndim != 2:
-                raise NotImplementedError(
-                    "WTConv1d computes the forward pass and the gradient of the input only: parameter gradients "
-                    "are not implemented. Freeze the parameters (requires_grad_(False)) or call the layer under "
-                    "torch.no_grad() / torch.inference_mode()")
             if trainable or x.requires_grad:
                 return _WTConvFunction.apply(x, self, *[p for p in ps if p is not None])
         return self._run(x)
+
+    def _param_grads(self, x, g):
+        """Gradients of all parameters for input x and output gradient g (full resolution).  A 1-D
+        signal is handed to the 2-D kernels as a one-row image."""
+        lib = _lib.load()
+        dev = x.device
+        K, L, code = self.kernel_size, self.wt_levels, _DTYPE_CODE[x.dtype]
+        if g.dtype != x.dtype:
+            g = g.to(x.dtype)
+        if self._ndim == 2:
+            B, C, H, W = x.shape
+            xstr, gstr = x.stride(), g.stride()
+        else:
+            B, C, W = x.shape
+            H = 1
+            xstr = (x.stride(0), x.stride(1), 0, x.stride(2))
+            gstr = (g.stride(0), g.stride(1), 0, g.stride(2))
+        n = lib.wtconv2d_pyramid_floats(B, C, H, W, L)
+        xp = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
+        gp = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
+        stats = torch.empty((1 + 4 * L, K * K + 1, C), dtype=torch.float32, device=dev)
+        xs = (ctypes.c_longlong * 4)(*xstr)
+        gs = (ctypes.c_longlong * 4)(*gstr)
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            _lib.check(lib.wtconv2d_pyramid(x.data_ptr(), xp.data_ptr(), B, C, H, W, L, code, xs, stream),
+                       "wtconv2d_pyramid")
+            _lib.check(lib.wtconv2d_pyramid(g.data_ptr(), gp.data_ptr(), B, C, H, W, L, code, gs, stream),
+                       "wtconv2d_pyramid")
+            _lib.check(lib.wtconv2d_weight_grad_stats(x.data_ptr(), g.data_ptr(), xp.data_ptr(), gp.data_ptr(),
+                                                      stats.data_ptr(), B, C, H, W, K, L, code, xs, gs, stream),
+                       "wtconv2d_weight_grad_stats")
+            ps = self._kernel_params()
+            hold = [p.detach().contiguous() if p is not None else None for p in ps]
+            grads = [torch.empty_like(h) if h is not None else None for h in hold]
+            s = torch.tensor(_SQRT_HALF, dtype=torch.float32)
+            tap = float(((s * s) if self._ndim == 2 else s).to(self.wt_filter.dtype))
+            arr_t = ctypes.c_void_p * max(L, 1)
+            ptrs = lambda ts, first: arr_t(*[ts[first + 2 * i].data_ptr() for i in range(L)])
+            _lib.check(lib.wtconv_param_grads(
+                self._ndim, C, K, L, _DTYPE_CODE[hold[0].dtype], tap, tap, stats.data_ptr(),
+                hold[0].data_ptr(), hold[1].data_ptr() if hold[1] is not None else None, hold[2].data_ptr(),
+                ptrs(hold, 3), ptrs(hold, 4),
+                grads[0].data_ptr(), grads[1].data_ptr() if grads[1] is not None else None, grads[2].data_ptr(),
+                ptrs(grads, 3), ptrs(grads, 4), stream), "wtconv_param_grads")
+        return grads
 
     def _grad_to_full_resolution(self, gy, in_shape):
         """Adjoint of the output stride: the gradient of the layer output before the stride."""
@@ -190,50 +231,13 @@ class _WTConvNd(nn.Module):
         return full
 
 
-def param_grads_from_stats(stats, params, gain):
-    """Parameter gradients of a 2-D layer from the correlation sums of wtconv2d_weight_grad_stats.
-
-    stats: (1+4L, K*K+1, C) fp32; params: the list [base_conv.weight, base_conv.bias or None,
-    base_scale.weight, wavelet_convs[0].weight, wavelet_scale[0].weight, ...]; gain: analysis tap *
-    synthesis tap of one level.  Returns gradients in the same order (None for a missing bias), in
-    the dtype of each parameter.
-    """
-    base_w, base_b, base_scale = params[0], params[1], params[2]
-    C = base_w.shape[0]
-    kk = base_w.shape[-1] * base_w.shape[-2]
-    st = stats.double()
-    corr0, sum_g = st[0, :kk].t(), st[0, kk]                         # (C, K*K), (C)
-    sc = base_scale.detach().double().reshape(C)
-    w0 = base_w.detach().double().reshape(C, kk)
-    grads = [(sc[:, None] * corr0).reshape(base_w.shape).to(base_w.dtype)]
-    d_scale = (w0 * corr0).sum(1)
-    if base_b is not None:
-        grads.append((sc * sum_g).to(base_b.dtype))
-        d_scale = d_scale + base_b.detach().double() * sum_g
-    else:
-        grads.append(None)
-    grads.append(d_scale.reshape(base_scale.shape).to(base_scale.dtype))
-    L = (len(params) - 3) // 2
-    g = 1.0
-    for l in range(L):
-        g *= gain
-        w, s = params[3 + 2 * l], params[4 + 2 * l]
-        corr = st[1 + 4 * l: 5 + 4 * l, :kk]                          # (4, K*K, C): [sub-band][tap][channel]
-        corr = corr.permute(2, 0, 1).reshape(4 * C, kk)               # row 4c+s, as the reference orders sub-bands
-        ws = w.detach().double().reshape(4 * C, kk)
-        ss = s.detach().double().reshape(4 * C)
-        grads.append((g * ss[:, None] * corr).reshape(w.shape).to(w.dtype))
-        grads.append((g * (ws * corr).sum(1)).reshape(s.shape).to(s.dtype))
-    return grads
-
-
 class _WTConvFunction(torch.autograd.Function):
     """The layer as one autograd node.  Input gradient: the Haar transform is orthogonal and odd sizes
     are padded and cropped at the same places, so the adjoint of the layer is the layer itself with
     every kernel flipped and the bias dropped -- one more forward call on the gradient, with the
-    adjoint parameter block.  Parameter gradients (2-D): correlation sums between the sub-band
+    adjoint parameter block.  Parameter gradients: correlation sums between the sub-band
     pyramids of the input and of the output gradient (wtconv2d_weight_grad_stats), scaled per
-    parameter in param_grads_from_stats."""
+    parameter by wtconv_param_grads."""
 
     @staticmethod
     def forward(ctx, x, module, *params):
@@ -293,33 +297,6 @@ class WTConv2d(_WTConvNd):
         if st:
             _lib.check(st, "wtconv2d_forward")
         return y
-
-    def _param_grads(self, x, g):
-        """Gradients of all parameters for input x and output gradient g (full resolution)."""
-        lib = _lib.load()
-        dev = x.device
-        B, C, H, W = x.shape
-        K, L, code = self.kernel_size, self.wt_levels, _DTYPE_CODE[x.dtype]
-        if g.dtype != x.dtype:
-            g = g.to(x.dtype)
-        n = lib.wtconv2d_pyramid_floats(B, C, H, W, L)
-        xp = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
-        gp = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
-        stats = torch.empty((1 + 4 * L, K * K + 1, C), dtype=torch.float32, device=dev)
-        xs = (ctypes.c_longlong * 4)(*x.stride())
-        gs = (ctypes.c_longlong * 4)(*g.stride())
-        with torch.cuda.device(dev):
-            stream = torch.cuda.current_stream(dev).cuda_stream
-            _lib.check(lib.wtconv2d_pyramid(x.data_ptr(), xp.data_ptr(), B, C, H, W, L, code, xs, stream),
-                       "wtconv2d_pyramid")
-            _lib.check(lib.wtconv2d_pyramid(g.data_ptr(), gp.data_ptr(), B, C, H, W, L, code, gs, stream),
-                       "wtconv2d_pyramid")
-            _lib.check(lib.wtconv2d_weight_grad_stats(x.data_ptr(), g.data_ptr(), xp.data_ptr(), gp.data_ptr(),
-                                                      stats.data_ptr(), B, C, H, W, K, L, code, xs, gs, stream),
-                       "wtconv2d_weight_grad_stats")
-        s = torch.tensor(_SQRT_HALF, dtype=torch.float32)
-        tap = float((s * s).to(self.wt_filter.dtype))
-        return param_grads_from_stats(stats, self._kernel_params(), tap * tap)
 
     def _plan_call(self, lib, x, s):
         B, C, H, W = x.shape
