@@ -66,3 +66,46 @@ def test_model_logits_match_oracle_layers():
     e_ours, e_oracle = nerr(a, b64), nerr(b32, b64)
     assert e_ours <= max(2.0 * e_oracle, 2e-5), f"vs fp64: ours {e_ours:.3e}, fp32 oracle {e_oracle:.3e}"
     assert nerr(a, b32) <= 5e-4, f"logit mismatch {nerr(a, b32):.3e}"
+
+
+@pytest.mark.gpu
+def test_model_training_step_matches_oracle_layers():
+    """One forward + backward of the harness: gradients through the 18 B200 layers (input and
+    parameters) against the same network with oracle layers under autograd, both in fp32."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import wtconv_b200
+    from wtconv_b200.wtconvnext_harness import WTConvNeXtTiny
+    dev = torch.device("cuda:0")
+    torch.manual_seed(1)
+    ours = WTConvNeXtTiny(wtconv_b200.WTConv2d)
+    with torch.no_grad():
+        for m in ours.modules():
+            if hasattr(m, "gamma"):
+                m.gamma.fill_(0.5)
+    ref = WTConvNeXtTiny(_OracleWTConv2d)
+    ref.load_state_dict({k.replace("conv_dw.", "conv_dw.inner."): v for k, v in ours.state_dict().items()})
+    ours, ref = ours.to(dev).train(), ref.to(dev).double().train()
+    x = torch.randn(2, 3, 224, 224, device=dev)
+    target = torch.randint(0, 1000, (2,), device=dev)
+    tf32 = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        loss_a = torch.nn.functional.cross_entropy(ours(x.contiguous(memory_format=torch.channels_last)), target)
+        loss_a.backward()
+        loss_b = torch.nn.functional.cross_entropy(ref(x.double()), target)
+        loss_b.backward()
+    finally:
+        torch.backends.cudnn.allow_tf32 = tf32
+    assert abs(float(loss_a) - float(loss_b)) <= 1e-4 * abs(float(loss_b))
+    ga = dict(ours.named_parameters())
+    checked = 0
+    for name, pb in ref.named_parameters():
+        if "filter" in name or pb.grad is None:
+            continue
+        pa = ga[name.replace("conv_dw.inner.", "conv_dw.")]
+        assert pa.grad is not None, name
+        err = float((pa.grad.double() - pb.grad).abs().max() / (pb.grad.abs().max() + 1e-30))
+        assert err <= 2e-3, f"{name}: {err:.3e}"        # fp32 network against its fp64 evaluation
+        checked += 1
+    assert checked >= 140
