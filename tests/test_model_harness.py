@@ -97,7 +97,7 @@ def test_model_training_step_matches_oracle_layers():
         loss_b.backward()
     finally:
         torch.backends.cudnn.allow_tf32 = tf32
-    assert abs(float(loss_a) - float(loss_b)) <= 1e-4 * abs(float(loss_b))
+    assert abs(float(loss_a.detach()) - float(loss_b.detach())) <= 1e-4 * abs(float(loss_b.detach()))
     ga = dict(ours.named_parameters())
     checked = 0
     for name, pb in ref.named_parameters():
