@@ -155,7 +155,7 @@ struct TileGeo {
 // ---------------------------------------------------------------------------
 template <typename T, typename XT, int K, bool FUSE_BASE>
 WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, int wy1, int wx1, int wy0, int wx0,
-                    int nrow0, int ncol0, bool has_r, T* __restrict__ out_tile) {
+                    int nrow0, int ncol0, bool has_r, T* __restrict__ out_tile, T* __restrict__ ytile) {
   constexpr int TH = 2, TW = 4;
   float acc[2 * TH][2 * TW];
   {
@@ -207,12 +207,25 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, in
 #pragma unroll
       for (int q = 0; q < 2 * TW; ++q) acc[i][q] += bias;
     conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc);
-    // finished pixels -> OUT[g]; the tile is allocated with the overhang of partial items
-    T* o = out_tile + g * p.oplane + (iy * 2 * TH) * p.opitch + ix * 2 * TW;
+    if (p.direct_store) {
+      // finished pixels -> y: `ytile` is the tile's first pixel of the group's first channel
+      const int ys2 = (int)p.ys[2], ys3 = (int)p.ys[3];
+      T* o = ytile + g + (iy * 2 * TH) * ys2 + (ix * 2 * TW) * ys3;
 #pragma unroll
-    for (int i = 0; i < 2 * TH; ++i) {
-      store4(o + i * p.opitch, acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-      store4(o + i * p.opitch + 4, acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+      for (int i = 0; i < 2 * TH; ++i) {
+        if (iy * 2 * TH + i >= nrow0) continue;
+#pragma unroll
+        for (int q = 0; q < 2 * TW; ++q)
+          if (ix * 2 * TW + q < ncol0) o[i * ys2 + q * ys3] = Elem<T>::from_f(acc[i][q]);
+      }
+    } else {
+      // finished pixels -> OUT[g]; the tile is allocated with the overhang of partial items
+      T* o = out_tile + g * p.oplane + (iy * 2 * TH) * p.opitch + ix * 2 * TW;
+#pragma unroll
+      for (int i = 0; i < 2 * TH; ++i) {
+        store4(o + i * p.opitch, acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        store4(o + i * p.opitch + 4, acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+      }
     }
   } else {
     float* out = sm.rec(0, g);
@@ -796,6 +809,9 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
+  T* ytile = nullptr;
+  if (FINAL && p.direct_store)
+    ytile = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1] + (size_t)tg.ty0 * p.ys[2] + (size_t)tg.tx0 * p.ys[3];
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
@@ -814,7 +830,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         if (g >= gc) continue;
         const int iy = t / ntx, ix = t - iy * ntx;
         top_item<T, XT, K, FINAL>(p, sm, g, iy, ix, wy1 + iy * 2, wx1 + ix * 4, wy0 + iy * 4, wx0 + ix * 8,
-                                  y0.n, x0g.n, has_r, out_tile);
+                                  y0.n, x0g.n, has_r, out_tile, ytile);
       }
     } else if (FINAL) {
       const int nty = cdiv(y0.n, 4), ntx = cdiv(x0g.n, 8);
@@ -831,7 +847,8 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
     }
   }
 
-  // ---- phase 4: write the tile
+  // ---- phase 4: write the tile (unless the items of phase 3 stored their pixels themselves)
+  if (FINAL && p.direct_store && d >= 1) return;
   WT_PHASE(nthr) {
     const int hn = tg.ty1 - tg.ty0, wn = tg.tx1 - tg.tx0;
     if (!FINAL) {

@@ -19,6 +19,8 @@ constexpr int kTiledLevels = 2;            // levels fused per stage when a plan
 
 // Tuning override of the threads per CTA (0 = automatic); process-wide, set by plan_layer.
 inline int& tuning_threads() { static int v = 0; return v; }
+// Direct stores from the top-level items of final stages (see Plan2d::direct_store); process-wide switch
+inline bool& direct_store_enabled() { static bool v = true; return v; }
 
 // thread-tile height for `n` rows out of a menu (largest first): cheapest padded
 // row count, with a small penalty for short tiles (they reuse fewer loaded rows)
@@ -125,7 +127,7 @@ inline long long layout_stage(Plan2d& p) {
   }
   p.ooff = (int)off;
   p.orows = p.opitch = p.oplane = 0;
-  if (p.has_base) {
+  if (p.has_base && !p.direct_store) {     // OUT staging tile (not needed when the items store to y themselves)
     const int tile_y = imin(p.TY, p.H), tile_x = imin(p.TX, p.W);
     p.orows = round_up(tile_y, 4);
     p.opitch = round_up(tile_x, 8);
@@ -296,6 +298,9 @@ inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int firs
     for (int i = 0; i < 4; ++i) p.ys[i] = ly.ys[i];
     p.y_cl = (ly.ys[1] == 1 && ly.C > 1) ? 1 : 0;
     p.y_vec = vec_bytes(ly.ys, G, ly.elem_size, ly.y_align);
+    // one barrier-separated phase less per tile: the quarter warp of an item (eight channels of
+    // one pixel) writes 16 contiguous bytes, neighbouring channel groups fill the sector in L2
+    p.direct_store = (direct_store_enabled() && nlev >= 1 && ly.stride == 1 && p.y_vec == 16 && (ly.C % G) == 0) ? 1 : 0;
   }
   return layout_stage(p);
 }

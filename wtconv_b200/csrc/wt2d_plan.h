@@ -62,6 +62,7 @@ struct Plan2d {
   long long xs[4], ys[4];
   int x_cl, y_cl;        // channel is the fastest-varying dimension
   int x_vec, y_vec;      // 16-byte channel chunks are legal for x / y
+  int direct_store;      // final stage, channels-last y, no stride: top-level items store their pixels themselves
 };
 
 // Geometry of one level along one axis for the tile [t0,t1), all in closed form so
