@@ -33,10 +33,18 @@ def _stale():
 
 
 def build(force=False):
+    """Builds under a file lock into a temporary name and renames it into place, so that test
+    workers running side by side never load a half-written library."""
     if force or _stale():
-        cmd = ["nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-fPIC", "-shared",
-               "-o", LIB, SRC]
-        subprocess.run(cmd, check=True, cwd=os.path.dirname(SRC))
+        import fcntl
+        with open(LIB + ".lock", "w") as lock:
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            if force or _stale():
+                tmp = f"{LIB}.{os.getpid()}.tmp"
+                cmd = ["nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-fPIC", "-shared",
+                       "-o", tmp, SRC]
+                subprocess.run(cmd, check=True, cwd=os.path.dirname(SRC))
+                os.replace(tmp, LIB)
     return LIB
 
 

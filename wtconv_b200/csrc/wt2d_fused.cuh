@@ -155,7 +155,8 @@ struct TileGeo {
 // ---------------------------------------------------------------------------
 template <typename T, typename XT, int K, bool FUSE_BASE>
 WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, int wy1, int wx1, int wy0, int wx0,
-                    int nrow0, int ncol0, bool has_r, T* __restrict__ out_tile, T* __restrict__ ytile) {
+                    int nrow0, int ncol0, bool has_r, T* __restrict__ out_tile, T* __restrict__ ytile,
+                    float* __restrict__ rtile) {
   constexpr int TH = 2, TW = 4;
   float acc[2 * TH][2 * TW];
   {
@@ -228,15 +229,35 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, in
       }
     }
   } else {
-    float* out = sm.rec(0, g);
-    const int opitch = p.rpitch[0];
+    if (p.direct_store) {
+      // reconstruction block -> the fp32 planes in global memory: `rtile` is the tile's first
+      // element of the group's first channel; rows of eight floats, 128-bit stores when whole
+      float* out = rtile + (size_t)g * ((size_t)p.H * p.W) + (size_t)(iy * 2 * TH) * p.W + ix * 2 * TW;
+      const bool whole = (ix * 2 * TW + 2 * TW <= ncol0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((p.W & 3) == 0);
 #pragma unroll
-    for (int i = 0; i < 2 * TH; ++i) {
-      const int oy = iy * 2 * TH + i;
+      for (int i = 0; i < 2 * TH; ++i) {
+        if (iy * 2 * TH + i >= nrow0) continue;
+        float* orow = out + (size_t)i * p.W;
+        if (whole) {
+          store4(orow, acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+          store4(orow + 4, acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        } else {
 #pragma unroll
-      for (int q = 0; q < 2 * TW; ++q) {
-        const int ox = ix * 2 * TW + q;
-        if (oy < nrow0 && ox < ncol0) out[oy * opitch + ox] = acc[i][q];
+          for (int q = 0; q < 2 * TW; ++q)
+            if (ix * 2 * TW + q < ncol0) orow[q] = acc[i][q];
+        }
+      }
+    } else {
+      float* out = sm.rec(0, g);
+      const int opitch = p.rpitch[0];
+#pragma unroll
+      for (int i = 0; i < 2 * TH; ++i) {
+        const int oy = iy * 2 * TH + i;
+#pragma unroll
+        for (int q = 0; q < 2 * TW; ++q) {
+          const int ox = ix * 2 * TW + q;
+          if (oy < nrow0 && ox < ncol0) out[oy * opitch + ox] = acc[i][q];
+        }
       }
     }
   }
@@ -810,8 +831,11 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   }
 
   T* ytile = nullptr;
+  float* rtile = nullptr;
   if (FINAL && p.direct_store)
     ytile = y + (size_t)nb * p.ys[0] + (size_t)c0 * p.ys[1] + (size_t)tg.ty0 * p.ys[2] + (size_t)tg.tx0 * p.ys[3];
+  if (!FINAL && p.direct_store)
+    rtile = rout + ((size_t)nb * p.C + c0) * (size_t)(p.H * p.W) + (size_t)tg.ty0 * p.W + tg.tx0;
   // ---- phase 3: top level of the stage (+ base convolution and bias); lanes run over the
   //      channels of the group first, so a quarter warp touches eight different planes
   WT_PHASE(nthr) {
@@ -830,7 +854,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
         if (g >= gc) continue;
         const int iy = t / ntx, ix = t - iy * ntx;
         top_item<T, XT, K, FINAL>(p, sm, g, iy, ix, wy1 + iy * 2, wx1 + ix * 4, wy0 + iy * 4, wx0 + ix * 8,
-                                  y0.n, x0g.n, has_r, out_tile, ytile);
+                                  y0.n, x0g.n, has_r, out_tile, ytile, rtile);
       }
     } else if (FINAL) {
       const int nty = cdiv(y0.n, 4), ntx = cdiv(x0g.n, 8);
@@ -848,7 +872,7 @@ WT_HD void wt2d_cta(const Plan2d& p, const T* __restrict__ x, T* __restrict__ y,
   }
 
   // ---- phase 4: write the tile (unless the items of phase 3 stored their pixels themselves)
-  if (FINAL && p.direct_store && d >= 1) return;
+  if (p.direct_store && d >= 1) return;
   WT_PHASE(nthr) {
     const int hn = tg.ty1 - tg.ty0, wn = tg.tx1 - tg.tx0;
     if (!FINAL) {

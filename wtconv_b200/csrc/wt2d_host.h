@@ -118,7 +118,7 @@ inline long long layout_stage(Plan2d& p) {
   for (int j = 0; j <= d; ++j) {
     // R_0 only exists in stages without a base convolution (their output); R_d only when
     // an earlier launch provides it
-    const bool needed = (j == 0) ? !p.has_base : ((j < d) || p.has_rin);
+    const bool needed = (j == 0) ? (!p.has_base && !p.direct_store) : ((j < d) || p.has_rin);
     p.rrows[j] = needed ? rext[0][j] : 0;
     p.rpitch[j] = needed ? round_up(rext[1][j], 4) : 0;
     p.rplane[j] = needed ? (int)pad_words((long long)p.rrows[j] * p.rpitch[j]) : 0;
@@ -300,7 +300,13 @@ inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int firs
     p.y_vec = vec_bytes(ly.ys, G, ly.elem_size, ly.y_align);
     // one barrier-separated phase less per tile: the quarter warp of an item (eight channels of
     // one pixel) writes 16 contiguous bytes, neighbouring channel groups fill the sector in L2
-    p.direct_store = (direct_store_enabled() && nlev >= 1 && ly.stride == 1 && p.y_vec == 16 && (ly.C % G) == 0) ? 1 : 0;
+    // (tiles across the whole plane width only: with narrower tiles the scattered stores of a large
+    // plane were measured 2.5x slower than the staged, coalesced ones)
+    p.direct_store = (direct_store_enabled() && nlev >= 1 && ly.stride == 1 && p.y_vec == 16 && (ly.C % G) == 0 &&
+                      TX >= W) ? 1 : 0;
+  } else {
+    // deep stages: the reconstruction block of an item goes straight to the fp32 planes
+    p.direct_store = (direct_store_enabled() && nlev >= 1 && TX >= W) ? 1 : 0;
   }
   return layout_stage(p);
 }
@@ -315,6 +321,7 @@ struct Tuning2d {
   int group = 0;         // channels per CTA
   int threads = 0;       // threads per CTA
   int regplane = 0;      // -1: never use the register-level kernels at the bottom; 1: also with other overrides
+  int direct = 0;        // -1: top-level items never store to global memory themselves
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -354,6 +361,7 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
 inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) {
   Chain2d ch;
   tuning_threads() = tune.threads;
+  direct_store_enabled() = tune.direct >= 0;
   // level sizes of the whole pyramid
   std::vector<int> Hl(ly.L + 1), Wl(ly.L + 1);
   Hl[0] = ly.H; Wl[0] = ly.W;
@@ -447,8 +455,11 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     const bool fits = !(tune.force_tiled == 2 && remaining > 0) && !(tune.force_tiled && q == 0) &&
                       remaining <= kMaxFused &&
                       plan_whole_plane(tmp, bytes, good, ly, Hl[q], Wl[q], q, remaining, q == 0, 0, tune.group, below);
-    // a deep stage (q > 0) that fits is always taken; the top stage only if it is efficient
-    if (fits && (good || q > 0 || remaining == 0)) {
+    // the top stage is taken only if it is efficient (two CTAs per SM, wide enough channel group);
+    // a deep stage also when only one CTA fits, as long as its plane is small: a large plane held
+    // whole by one CTA per SM loses more to idle SMs than its tiled split costs
+    const bool small_plane = (long long)Hl[q] * Wl[q] <= 64 * 64;
+    if (fits && (good || (q > 0 && small_plane) || remaining == 0)) {
       cuts.push_back({q, remaining, true});
       break;
     }
