@@ -109,3 +109,27 @@ def test_model_training_step_matches_oracle_layers():
         assert err <= 2e-3, f"{name}: {err:.3e}"        # fp32 network against its fp64 evaluation
         checked += 1
     assert checked >= 140
+
+
+@pytest.mark.gpu
+def test_captured_forward_replays_eager_result():
+    """The CUDA-graph replay of the whole model gives the logits of the eager forward (bf16: normalised
+    max error <= 2e-2; the library GEMMs may pick another algorithm under capture), for more than one
+    batch through the same graph, and rejects another shape."""
+    import wtconv_b200
+    from wtconv_b200.wtconvnext_harness import CapturedForward, WTConvNeXtTiny
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    model = WTConvNeXtTiny(wtconv_b200.WTConv2d).to(dev).to(torch.bfloat16).eval()
+    model = model.to(memory_format=torch.channels_last)
+    xs = [torch.randn(2, 3, 224, 224, device=dev, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+          for _ in range(2)]
+    fwd = CapturedForward(model, xs[0])
+    with torch.no_grad():
+        for x in (xs[1], xs[0], xs[1]):
+            want = model(x)
+            got = fwd(x).clone()
+            err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+            assert err <= 2e-2, err
+    with pytest.raises(ValueError):
+        fwd(xs[0][:1])

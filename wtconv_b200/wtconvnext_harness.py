@@ -78,3 +78,39 @@ class WTConvNeXtTiny(nn.Module):
     def forward(self, x):
         x = self.stages(self.stem(x))
         return self.head_fc(self.head_norm(x.mean((2, 3))))
+
+
+class CapturedForward:
+    """Whole-model inference forward captured once into a CUDA graph and replayed per batch.
+
+    The WTConv2d layers plan their launch chain on the host for every call; at small batches that
+    planning and the 18 x (3..6) launches cost more than the kernels.  Capturing the forward of a fixed
+    input shape removes all of it: `__call__` copies the batch into the graph's input buffer, replays,
+    and returns the graph's output buffer (valid until the next call).  Parameters are read in place
+    by the replay; the folded parameter blocks of the WTConv2d layers are NOT refreshed by it, so
+    capture again after changing weights.
+    """
+
+    def __init__(self, model: nn.Module, example: torch.Tensor, warmup: int = 3):
+        if not example.is_cuda:
+            raise ValueError("CapturedForward needs a CUDA example input")
+        self.model = model
+        self.static_in = example.clone(memory_format=torch.preserve_format)
+        side = torch.cuda.Stream(device=example.device)
+        side.wait_stream(torch.cuda.current_stream(example.device))
+        with torch.no_grad(), torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):       # packs parameters, plans chains, sets kernel attributes
+                model(self.static_in)
+        torch.cuda.current_stream(example.device).wait_stream(side)
+        torch.cuda.synchronize(example.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.static_out = model(self.static_in)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape != self.static_in.shape or x.dtype != self.static_in.dtype:
+            raise ValueError(f"captured for {tuple(self.static_in.shape)} {self.static_in.dtype}, "
+                             f"got {tuple(x.shape)} {x.dtype}")
+        self.static_in.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.static_out
