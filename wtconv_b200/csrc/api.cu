@@ -47,16 +47,16 @@ cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, cons
   }
 }
 
-// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group,threads,regplane,direct"
+// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group,threads,regplane,direct,deep_group"
 // (integers, 0 = automatic).  Read once; absent in normal use.
 const Tuning2d& env_tuning() {
   static const Tuning2d t = [] {
     Tuning2d v;
     if (const char* e = getenv("WTCONV_TUNE")) {
-      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0, r = 0, ds = 0;
-      sscanf(e, "%d,%d,%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t, &r, &ds);
+      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0, r = 0, ds = 0, dg = 0;
+      sscanf(e, "%d,%d,%d,%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t, &r, &ds, &dg);
       v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g; v.threads = t; v.regplane = r;
-      v.direct = ds;
+      v.direct = ds; v.deep_group = dg;
     }
     return v;
   }();

@@ -322,6 +322,7 @@ struct Tuning2d {
   int threads = 0;       // threads per CTA
   int regplane = 0;      // -1: never use the register-level kernels at the bottom; 1: also with other overrides
   int direct = 0;        // -1: top-level items never store to global memory themselves
+  int deep_group = 0;    // channel group of whole-plane stages below the top (0: automatic)
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -506,7 +507,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     if (c.whole) {
       bool good = false;
       if (!plan_whole_plane(st.plan, st.smem_bytes, good, ly, H, W, c.first, c.nlev, final_stage, in_shift,
-                            final_stage ? tune.group : 0, has_rin)) {
+                            final_stage ? tune.group : tune.deep_group, has_rin)) {
         ch.status = -6; return ch;
       }
     } else {
