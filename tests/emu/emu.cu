@@ -204,6 +204,7 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
   tune.tile_levels = g_force_levels;
   tune.group = g_force_group;
   tune.regplane = g_force_regplane;
+  tune.cl = -1;   // the TMA-fed channels-last stage has no host form; the emulation covers the other kernels
   Chain2d ch = plan_layer(ly, tune);
   if (ch.status) return ch.status;
   std::vector<float> ws((size_t)ch.scratch_floats + 4, 1.0e30f);

@@ -53,8 +53,9 @@ const Tuning2d& env_tuning() {
   static const Tuning2d t = [] {
     Tuning2d v;
     if (const char* e = getenv("WTCONV_TUNE")) {
-      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0, r = 0, ds = 0, dg = 0;
-      sscanf(e, "%d,%d,%d,%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t, &r, &ds, &dg);
+      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0, r = 0, ds = 0, dg = 0, cl = 0;
+      sscanf(e, "%d,%d,%d,%d,%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t, &r, &ds, &dg, &cl);
+      v.cl = cl;
       v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g; v.threads = t; v.regplane = r;
       v.direct = ds; v.deep_group = dg;
     }
@@ -390,6 +391,9 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
         break;
       case 2:
         e = launch_quad(sg.quad, in_dtype, xin, final_stage ? y : nullptr, rin, rout, packed, (size_t)sg.smem_bytes, cs);
+        break;
+      case 3:
+        e = launch_cl_level(sg.cl, in_dtype, xin, rin, y, packed, nullptr, cs);
         break;
       default:
         e = launch_wt2d(sg.plan, in_dtype, xin, final_stage ? y : nullptr, packed, rin, rout, (size_t)sg.smem_bytes, cs);

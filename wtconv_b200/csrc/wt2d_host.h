@@ -6,6 +6,7 @@
 
 #include <vector>
 
+#include "wt2d_cl_host.h"
 #include "wt2d_plan.h"
 #include "wt2d_quad.cuh"
 #include "wt2d_regplane.cuh"
@@ -221,10 +222,11 @@ inline long long plan_quad(QuadPlane& a, int B, int C, int K, int L, int q, int 
 
 struct Stage2d {
   // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg),
-  // 2: four-warp 14 x 14 level kernel (quad)
+  // 2: four-warp 14 x 14 level kernel (quad), 3: channels-last level stage (cl)
   int kind = 0;
   RegPlane reg;
   QuadPlane quad;
+  ClStage cl;
   Plan2d plan = Plan2d();
   long long xin_off;   // fp32 low-pass planes read as input (floats into scratch), -1: the layer input
   long long rin_off;   // reconstruction of the deeper levels read, -1: none
@@ -326,6 +328,7 @@ struct Tuning2d {
   int regplane = 0;      // -1: never use the register-level kernels at the bottom; 1: also with other overrides
   int direct = 0;        // -1: top-level items never store to global memory themselves
   int deep_group = 0;    // channel group of whole-plane stages below the top (0: automatic)
+  int cl = 0;            // -1: never use the channels-last level stage
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -361,6 +364,25 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
   return true;
 }
 
+// The channels-last level stage (wt2d_cl.cuh) reads its input through a tensor map: channel
+// stride 1, every other stride and the base address multiples of 16 bytes.
+inline bool cl_stage_supported(const Layer2d& ly) {
+  if (ly.K != 5 || ly.stride != 1 || ly.C < 8) return false;
+  if (ly.xs[1] != 1 || ly.ys[1] != 1) return false;
+  if (ly.x_align < 16) return false;
+  for (int i = 0; i < 4; ++i)
+    if (i != 1 && ((ly.xs[i] * ly.elem_size) % 16 != 0)) return false;
+  return true;
+}
+
+// Tile configuration of the channels-last level stage for a W-wide plane (see launch_shape)
+inline int cl_config(int W) {
+  if (W <= 8) return 4;
+  if (W <= 16) return 3;
+  if (W <= 32) return 2;
+  return 1;
+}
+
 // Builds the launch chain of one layer.
 inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) {
   Chain2d ch;
@@ -374,6 +396,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // Bottom of the pyramid: when the plane of some level q is small enough for the
   // register-resident kernel (channels-last tensors, every remaining level), that kernel
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
+  const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly);
   int qreg = -1;
   const bool untuned = !tune.force_tiled && !tune.tile_y && !tune.tile_x && !tune.tile_levels && !tune.group;
   if ((untuned || tune.regplane > 0) && tune.regplane >= 0 && ly.xs[1] == 1 && ly.C > 1) {
@@ -469,6 +492,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     }
     int nlev = tune.tile_levels > 0 ? imin(tune.tile_levels, kMaxFused)
                                     : ((Hl[q] > 128 || Wl[q] > 128) ? kTiledLevels : 1);
+    if (use_cl && q == 0) nlev = 1;    // the channels-last stage takes exactly the top level
     nlev = imin(remaining, nlev);
     if (fits && nlev == remaining) {   // nothing to split off below: keep the whole-plane stage
       cuts.push_back({q, remaining, true});
@@ -507,6 +531,27 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     const bool has_rin = (i + 1 < (int)cuts.size()) || below;
     const int in_shift = (direct && i == 1) ? c.first : 0;
     const int H = Hl[c.first], W = Wl[c.first];
+    if (use_cl && final_stage && c.nlev == 1) {
+      st.kind = 3;
+      ClStage& s = st.cl;
+      s.B = ly.B; s.C = ly.C; s.H = H; s.W = W; s.K = ly.K;
+      s.level = 0; s.has_base = 1;
+      s.config = cl_config(W);
+      s.wstride = packed_channel_floats(ly.K, 2, ly.L);
+      s.tapset = tapset_floats(ly.K, 2);
+      const int Hh = Hl[1], Wh = Wl[1];
+      for (int k = 0; k < 4; ++k) { s.xs[k] = ly.xs[k]; s.os[k] = ly.ys[k]; }
+      s.rs[0] = (long long)ly.C * Hh * Wh; s.rs[1] = (long long)Hh * Wh; s.rs[2] = Wh; s.rs[3] = 1;
+      s.rin_vec = 0;
+      const int pair_bytes = 2 * ly.elem_size;
+      s.out_vec = (ly.y_align >= pair_bytes && (ly.ys[0] % 2) == 0 && (ly.ys[2] % 2) == 0 && (ly.ys[3] % 2) == 0) ? 1 : 0;
+      st.smem_bytes = 0;
+      st.xin_off = -1;
+      st.rin_off = has_rin ? roff[i + 1] : -1;
+      st.rout_off = -1;
+      ch.stages.push_back(st);
+      continue;
+    }
     if (c.whole) {
       bool good = false;
       if (!plan_whole_plane(st.plan, st.smem_bytes, good, ly, H, W, c.first, c.nlev, final_stage, in_shift,
