@@ -162,6 +162,7 @@ int emu_pack_params(int ndim, int C, int K, int L, int param_dtype, double ana_t
   a.tapset = tapset_floats(K, ndim);
   a.subbands = (ndim == 2) ? 4 : 2;
   a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  a.cl_off = 0;
   double g = 1.0;
   for (int l = 0; l < L; ++l) {
     a.wavelet_w[l] = wavelet_w[l];

@@ -154,6 +154,7 @@ const char* wtconv_status_string(int status) {
 
 size_t wtconv_packed_param_floats(int ndim, int C, int K, int L) {
   if ((ndim != 1 && ndim != 2) || C <= 0 || K < 1 || L < 0) return 0;
+  if (ndim == 2) return (size_t)(cl_param_offset(C, K, L) + cl_param_floats(C, K, L));
   return (size_t)C * packed_channel_floats(K, ndim, L);
 }
 
@@ -171,6 +172,7 @@ static int pack_params_impl(int adjoint, int ndim, int C, int K, int L, int para
   a.tapset = tapset_floats(K, ndim);
   a.subbands = (ndim == 2) ? 4 : 2;
   a.base_w = base_w; a.base_b = base_b; a.base_scale = base_scale;
+  a.cl_off = (ndim == 2) ? cl_param_offset(C, K, L) : 0;
   double g = 1.0;
   for (int l = 0; l < kMaxLevels; ++l) {
     a.wavelet_w[l] = nullptr; a.wavelet_scale[l] = nullptr; a.gain[l] = 0.0;
@@ -392,9 +394,17 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
       case 2:
         e = launch_quad(sg.quad, in_dtype, xin, final_stage ? y : nullptr, rin, rout, packed, (size_t)sg.smem_bytes, cs);
         break;
-      case 3:
-        e = launch_cl_level(sg.cl, in_dtype, xin, rin, y, packed, nullptr, cs);
+      case 3:   // input: the layer input or a low-pass plane in the layer's type; output: y or fp32 planes
+        e = launch_cl_level(sg.cl, dtype, xin, rin, final_stage ? y : static_cast<void*>(rout), packed, nullptr, cs);
         break;
+      case 4:   // input: the sub-bands of level 2 in the layer's type
+        e = launch_cl_deep(sg.deep, ly.K, dtype, xin, packed, rout, nullptr, cs);
+        break;
+      case 5: {
+        const int xv = (ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0;
+        e = launch_cl_pyramid(dtype, x, ly.xs, xv, ly.B, ly.C, ly.H, ly.W, rout, cs);
+        break;
+      }
       default:
         e = launch_wt2d(sg.plan, in_dtype, xin, final_stage ? y : nullptr, packed, rin, rout, (size_t)sg.smem_bytes, cs);
         break;

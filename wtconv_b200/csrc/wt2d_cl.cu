@@ -1,6 +1,7 @@
 // Host side of the channels-last level stage: configuration table, tensor map, launch.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "wt2d_cl.cuh"
@@ -34,6 +35,20 @@ template <> struct TmaType<float> { static constexpr CUtensorMapDataType v = CU_
 template <> struct TmaType<__nv_bfloat16> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
 template <> struct TmaType<__half> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; };
 
+// Tensor map of a channels-last plane set (dimensions channel, column, row, sample) with the given box
+template <typename T>
+cudaError_t make_map(CUtensorMap& map, const void* x, int B, int C, int H, int W, const long long* xs, int box_w, int box_h) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cudaErrorNotSupported;
+  const cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t gstr[3] = {(cuuint64_t)xs[3] * sizeof(T), (cuuint64_t)xs[2] * sizeof(T), (cuuint64_t)xs[0] * sizeof(T)};
+  const cuuint32_t box[4] = {(cuuint32_t)kClGroup, (cuuint32_t)box_w, (cuuint32_t)box_h, 1u};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(&map, TmaType<T>::v, 4, const_cast<void*>(x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MINB>
 cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* out, const float* packed, int* status,
                        cudaStream_t stream) {
@@ -41,19 +56,9 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   if constexpr (G::smem_bytes > (size_t)kMaxDynamicSmem) {
     return cudaErrorInvalidConfiguration;   // the planner never picks a configuration that does not fit
   } else {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return cudaErrorNotSupported;
   CUtensorMap map;
-  const cuuint64_t gdim[4] = {(cuuint64_t)s.C, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.B};
-  const cuuint64_t gstr[3] = {(cuuint64_t)s.xs[3] * sizeof(T), (cuuint64_t)s.xs[2] * sizeof(T),
-                              (cuuint64_t)s.xs[0] * sizeof(T)};
-  const cuuint32_t box[4] = {(cuuint32_t)kClGroup, (cuuint32_t)G::XC, (cuuint32_t)2, (cuuint32_t)NS};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(&map, TmaType<T>::v, 4, const_cast<void*>(x), gdim, gstr, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-
+  cudaError_t me = make_map<T>(map, x, s.B, s.C, s.H, s.W, s.xs, G::XC, G::BOXR);
+  if (me != cudaSuccess) return me;
   ClArgs a;
   a.B = s.B; a.C = s.C; a.H = s.H; a.W = s.W;
   a.Hh = (s.H + 1) / 2; a.Wh = (s.W + 1) / 2;
@@ -61,12 +66,15 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   a.nbx = cdiv(a.Wh, NTX * kClCW);
   a.ngroups = cdiv(s.C, kClGroup);
   a.nslot_groups = cdiv(s.B, NS);
-  a.packed = packed; a.wstride = s.wstride; a.tapset = s.tapset; a.level = s.level;
+  a.packed = packed; a.cl_off = s.cl_off; a.nlevels = s.nlevels; a.level = s.level;
   a.rin = rin;
   a.out = out;
   for (int i = 0; i < 4; ++i) { a.rs[i] = s.rs[i]; a.os[i] = s.os[i]; }
-  a.out_vec = s.out_vec; a.rin_vec = s.rin_vec;
+  a.out_vec = s.out_vec; a.rin_vec = s.rin_vec; a.rin_scale = s.rin_scale;
   a.status = status;
+#ifdef WT_CL_TIMING
+  if (const char* e = getenv("WT_CL_DBG")) a.status = reinterpret_cast<int*>(strtoull(e, nullptr, 16));
+#endif
 
   auto kern = wt2d_cl_level_kernel<T, TO, K, NTY, NTX, NS, BASE, MINB>;
   constexpr size_t smem = G::smem_bytes;
@@ -91,7 +99,65 @@ cudaError_t launch_shape(const ClStage& s, const void* x, const float* rin, void
   }
 }
 
+template <typename T, int K>
+cudaError_t launch_deep_t(const ClDeepArgs& a0, const void* s2, const float* packed, float* rout, int* status,
+                          cudaStream_t stream) {
+  // tensor map over (channel, column, row, sample * 4 + sub-band) of the dense sub-band planes
+  const long long xs[4] = {(long long)a0.h[1] * a0.w[1] * a0.C, 1, (long long)a0.w[1] * a0.C, a0.C};
+  CUtensorMap map;
+  cudaError_t me = make_map<T>(map, s2, a0.B * 4, a0.C, a0.h[1], a0.w[1], xs, a0.spitch[1], a0.srows[1]);
+  if (me != cudaSuccess) return me;
+  ClDeepArgs a = a0;
+  a.packed = packed; a.rout = rout; a.status = status;
+#ifdef WT_CL_TIMING
+  if (const char* e = getenv("WT_CL_DBG2")) a.status = reinterpret_cast<int*>(strtoull(e, nullptr, 16));
+#endif
+  auto kern = wt2d_cl_deep_kernel<T, K>;
+  static bool done[kMaxDevices] = {false};
+  cudaError_t e = allow_full_smem(kern, done);
+  if (e != cudaSuccess) return e;
+  const dim3 grid((unsigned)cdiv(a.C, kClGroup), (unsigned)cdiv(a.B, a.ns));
+  kern<<<grid, kClDeepThreads, (size_t)a.smem_bytes, stream>>>(map, a);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_pyramid_t(const void* x, const long long* xs, int x_vec, int B, int C, int H, int W, void* s2,
+                             cudaStream_t stream) {
+  ClPyramidArgs a;
+  a.x = x;
+  for (int i = 0; i < 4; ++i) a.xs[i] = xs[i];
+  a.x_vec = x_vec;
+  a.B = B; a.C = C; a.H = H; a.W = W;
+  a.h2 = ((H + 1) / 2 + 1) / 2; a.w2 = ((W + 1) / 2 + 1) / 2;
+  a.s2 = s2;
+  a.total = (long long)B * a.h2 * a.w2 * ((C + 1) / 2);
+  const long long want = (a.total + 255) / 256;
+  const int blocks = (int)(want > 148 * 64 ? 148 * 64 : want);
+  wt2d_cl_pyramid_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
 }  // namespace
+
+cudaError_t launch_cl_pyramid(int dtype, const void* x, const long long* xs, int x_vec, int B, int C, int H, int W,
+                              void* s2, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return launch_pyramid_t<float>(x, xs, x_vec, B, C, H, W, s2, st);
+    case 1: return launch_pyramid_t<__nv_bfloat16>(x, xs, x_vec, B, C, H, W, s2, st);
+    default: return launch_pyramid_t<__half>(x, xs, x_vec, B, C, H, W, s2, st);
+  }
+}
+
+cudaError_t launch_cl_deep(const ClDeepArgs& a, int K, int dtype, const void* s2, const float* packed, float* rout,
+                           int* status, cudaStream_t st) {
+  if (K != 5) return cudaErrorNotSupported;
+  switch (dtype) {
+    case 0: return launch_deep_t<float, 5>(a, s2, packed, rout, status, st);
+    case 1: return launch_deep_t<__nv_bfloat16, 5>(a, s2, packed, rout, status, st);
+    default: return launch_deep_t<__half, 5>(a, s2, packed, rout, status, st);
+  }
+}
 
 cudaError_t launch_cl_level(const ClStage& s, int dtype, const void* x, const float* rin, void* out,
                             const float* packed, int* status, cudaStream_t st) {
@@ -103,7 +169,11 @@ cudaError_t launch_cl_level(const ClStage& s, int dtype, const void* x, const fl
       default: return launch_shape<__half, __half, 5, true>(s, x, rin, out, packed, status, st);
     }
   }
-  return cudaErrorNotSupported;
+  switch (dtype) {
+    case 0: return launch_shape<float, float, 5, false>(s, x, rin, out, packed, status, st);
+    case 1: return launch_shape<__nv_bfloat16, float, 5, false>(s, x, rin, out, packed, status, st);
+    default: return launch_shape<__half, float, 5, false>(s, x, rin, out, packed, status, st);
+  }
 }
 
 }  // namespace wt

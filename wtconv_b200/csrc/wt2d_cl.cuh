@@ -34,13 +34,10 @@
 #include <cuda_runtime.h>
 
 #include "wt_common.h"
+#include "wt2d_cl_host.h"
 
 namespace wt {
 
-constexpr int kClGroup = 16;          // channels per plane slot
-constexpr int kClLanes = 8;           // lanes (channel pairs) per thread tile
-constexpr int kClRH = 2, kClCW = 4;   // sub-band positions per thread tile
-constexpr int kClStages = 3;          // TMA chunks in flight
 constexpr unsigned kClWaitSpins = 1u << 22;   // bound of every mbarrier wait
 
 struct ClArgs {
@@ -50,8 +47,8 @@ struct ClArgs {
   int ngroups;             // channel groups of 16
   int nslot_groups;        // ceil(B / NS)
   const float* packed;     // folded parameters (wtconv_pack_params layout)
-  int wstride;             // floats per channel
-  int tapset;              // floats per tap set
+  long long cl_off;        // floats from `packed` to the channels-last parameter copy
+  int nlevels;             // wavelet levels of the layer (tap sets per channel group = 1 + 4 * nlevels)
   int level;               // 0-based level of this stage inside the packed block
   const float* rin;        // deeper reconstruction (fp32), may be null
   long long rs[4];         // its strides in floats: n, c, h, w
@@ -59,6 +56,7 @@ struct ClArgs {
   long long os[4];         // its strides in elements: n, c, h, w
   int out_vec;             // 1: channel pairs may be stored as one word
   int rin_vec;             // 1: channel pairs of rin may be loaded as one 8-byte word
+  float rin_scale;         // factor applied to rin: 1/2 for a reconstruction at the reference's scale
   int* status;             // device word that receives a nonzero code when a wait gives up
 };
 
@@ -102,25 +100,90 @@ __device__ __forceinline__ void cl_tma_load4(void* dst, const CUtensorMap* map, 
       : "memory");
 }
 
+// One 2 x 2 Haar analysis step at the reference's scale (wavelet.py:27-30 with tap 1/2):
+// sb = {LL, LH, HL, HH} = 1/2 {a+b+c+d, a+b-c-d, a-b+c-d, a-b-c+d}
+__device__ __forceinline__ void cl_haar(float2 a, float2 b, float2 c, float2 d, float2 (&sb)[4]) {
+  const float2 h = make_float2(0.5f, 0.5f), mh = make_float2(-0.5f, -0.5f);
+  const float2 pp = cl_add2(a, b), qq = cl_sub2(a, b), uu = cl_add2(c, d), vv = cl_sub2(c, d);
+  const float2 hu = __fmul2_rn(uu, h), hv = __fmul2_rn(vv, h);
+  sb[0] = cl_fma2(pp, h, hu);
+  sb[1] = cl_fma2(pp, h, __fmul2_rn(uu, mh));
+  sb[2] = cl_fma2(qq, h, hv);
+  sb[3] = cl_fma2(qq, h, __fmul2_rn(vv, mh));
+}
+
+// plain bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`
+__device__ __forceinline__ void cl_bulk_load(void* dst, const void* src, unsigned bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(cl_smem_addr(dst)), "l"(src), "r"(bytes), "r"(cl_smem_addr(bar))
+               : "memory");
+}
+
 // channel pair of a staged pixel -> fp32 pair
 template <typename T> struct ClPair;
 template <> struct ClPair<float> {
+  typedef float2 raw_t;
+  static __device__ __forceinline__ raw_t load_raw(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ float2 widen(raw_t r) { return r; }
+  static __device__ __forceinline__ void store_raw(float* p, raw_t r) { *reinterpret_cast<float2*>(p) = r; }
+  // channel pair from global memory; `both`: the second channel exists
+  static __device__ __forceinline__ raw_t load_global(const float* p, bool valid, bool vec, bool both) {
+    raw_t r = make_float2(0.f, 0.f);
+    if (valid) {
+      if (vec) r = __ldg(reinterpret_cast<const float2*>(p));
+      else { r.x = __ldg(p); if (both) r.y = __ldg(p + 1); }
+    }
+    return r;
+  }
   static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
   static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
 };
 template <> struct ClPair<__nv_bfloat16> {
-  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
-    const unsigned u = *reinterpret_cast<const unsigned*>(p);
-    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  typedef unsigned raw_t;
+  static __device__ __forceinline__ raw_t load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned*>(p); }
+  // bf16 -> fp32 is a move of the 16 bits into the upper half: two byte permutes (integer pipe).
+  // Written as prmt so that the compiler does not turn shift/mask into conversion instructions,
+  // which issue at a fraction of the integer rate.
+  static __device__ __forceinline__ float2 widen(raw_t u) {
+    unsigned lo, hi;
+    asm("prmt.b32 %0, %1, 0, 0x1044;" : "=r"(lo) : "r"(u));
+    asm("prmt.b32 %0, %1, 0, 0x3244;" : "=r"(hi) : "r"(u));
+    return make_float2(__uint_as_float(lo), __uint_as_float(hi));
   }
+  static __device__ __forceinline__ void store_raw(__nv_bfloat16* p, raw_t r) { *reinterpret_cast<unsigned*>(p) = r; }
+  static __device__ __forceinline__ raw_t load_global(const __nv_bfloat16* p, bool valid, bool vec, bool both) {
+    raw_t r = 0u;
+    if (valid) {
+      if (vec) r = __ldg(reinterpret_cast<const unsigned*>(p));
+      else {
+        r = (unsigned)__ldg(reinterpret_cast<const unsigned short*>(p));
+        if (both) r |= ((unsigned)__ldg(reinterpret_cast<const unsigned short*>(p) + 1) << 16);
+      }
+    }
+    return r;
+  }
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) { return widen(load_raw(p)); }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __float22bfloat162_rn(v);
   }
 };
 template <> struct ClPair<__half> {
-  static __device__ __forceinline__ float2 load(const __half* p) {
-    return __half22float2(*reinterpret_cast<const __half2*>(p));
+  typedef unsigned raw_t;
+  static __device__ __forceinline__ raw_t load_raw(const __half* p) { return *reinterpret_cast<const unsigned*>(p); }
+  static __device__ __forceinline__ float2 widen(raw_t u) { return __half22float2(*reinterpret_cast<const __half2*>(&u)); }
+  static __device__ __forceinline__ void store_raw(__half* p, raw_t r) { *reinterpret_cast<unsigned*>(p) = r; }
+  static __device__ __forceinline__ raw_t load_global(const __half* p, bool valid, bool vec, bool both) {
+    raw_t r = 0u;
+    if (valid) {
+      if (vec) r = __ldg(reinterpret_cast<const unsigned*>(p));
+      else {
+        r = (unsigned)__ldg(reinterpret_cast<const unsigned short*>(p));
+        if (both) r |= ((unsigned)__ldg(reinterpret_cast<const unsigned short*>(p) + 1) << 16);
+      }
+    }
+    return r;
   }
+  static __device__ __forceinline__ float2 load(const __half* p) { return widen(load_raw(p)); }
   static __device__ __forceinline__ void store(__half* p, float2 v) {
     *reinterpret_cast<__half2*>(p) = __float22half2_rn(v);
   }
@@ -134,22 +197,21 @@ struct ClGeo {
   static constexpr int SR = NTY * kClRH + 2 * HS;           // sub-band frame rows
   static constexpr int SC = ((NTX * kClCW + 2 * HS + 3) / 4) * 4;   // sub-band frame columns (whole rotation groups)
   static constexpr int XR = 2 * SR, XC = 2 * SC;            // pixel frame delivered by the TMA chunks
-  static constexpr int XRA = XR - 2 * HS;                   // pixel rows kept for the base convolution (frame rows HS..)
-  static constexpr int NCHUNK = SR;                         // one sub-band row (two pixel rows) per chunk
-  static constexpr int NT = NTY * NTX * NS * kClLanes;      // threads per CTA
+  static constexpr int NBOX = 4;                            // TMA boxes per slot, stacked along the rows
+  static constexpr int BOXR = XR / NBOX;                    // pixel rows per box
+  static_assert(XR % NBOX == 0, "the pixel frame is a whole number of boxes");
+  static constexpr int NT = (NTY * NTX * NS * kClLanes + 31) / 32 * 32;   // threads per CTA (whole warps)
   static constexpr int TAPS = K * K + 1;                    // staged floats per tap set and channel (last: bias slot)
   static constexpr int PX = kClGroup;                       // elements of T per pixel
   static constexpr int SL = 128 / (kClGroup * (int)sizeof(T));   // pixels per 128-byte line
   static constexpr int SUB = SR * SC * PX;                  // elements per sub-band of a slot
   static constexpr int SLOT_S = 4 * SUB;
-  static constexpr int SLOT_X = XRA * XC * PX;
+  static constexpr int SLOT_X = XR * XC * PX;
   static constexpr size_t s_bytes = (size_t)NS * SLOT_S * sizeof(T);
   static constexpr size_t x_bytes = (size_t)NS * SLOT_X * sizeof(T);
   static constexpr size_t w_bytes = (size_t)5 * TAPS * kClLanes * sizeof(float2);
-  static constexpr size_t chunk_elems = (size_t)NS * 2 * XC * kClGroup;
-  static constexpr size_t stage_bytes = ((chunk_elems * sizeof(T) + 127) / 128) * 128;
-  static constexpr size_t smem_bytes =
-      128 /* alignment slack */ + s_bytes + x_bytes + w_bytes + kClStages * stage_bytes + 64 /* barriers */;
+  static constexpr size_t box_bytes = (size_t)BOXR * XC * PX * sizeof(T);
+  static constexpr size_t smem_bytes = 128 /* alignment slack */ + s_bytes + x_bytes + w_bytes + 64 /* barriers */;
 };
 
 // Rotation swizzle.  A pixel (16 channels) takes 128/SL bytes; the SL thread tiles served by one
@@ -233,21 +295,25 @@ __device__ __forceinline__ void cl_base_conv(float2 (&out)[2 * kClRH][2 * kClCW]
 // for the layer output, float for a reconstruction handed to the next shallower level); BASE: add
 // the base path.
 template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MINB>
-__global__ void __launch_bounds__(NTY* NTX* NS* kClLanes, MINB)
+__global__ void __launch_bounds__((NTY * NTX * NS * kClLanes + 31) / 32 * 32, MINB)
 wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ ClArgs a) {
 #ifdef __CUDA_ARCH__
   typedef ClGeo<T, K, NTY, NTX, NS> G;
-  constexpr int SC = G::SC, HS = G::HS, SL = G::SL, XC = G::XC;
+  typedef typename ClPair<T>::raw_t raw_t;
+  constexpr int SC = G::SC, SR = G::SR, HS = G::HS, SL = G::SL, XC = G::XC;
   static_assert(kClRH == 2 && kClCW == 4, "the swizzle assumes 2 x 4 thread tiles");
   extern __shared__ unsigned char cl_smem_raw[];
   unsigned char* sm = cl_smem_raw + ((128u - (cl_smem_addr(cl_smem_raw) & 127u)) & 127u);
-  T* S = reinterpret_cast<T*>(sm);
-  T* XT = reinterpret_cast<T*>(sm + G::s_bytes);
-  float2* Wsm = reinterpret_cast<float2*>(sm + G::s_bytes + G::x_bytes);
-  unsigned char* stage0 = sm + G::s_bytes + G::x_bytes + G::w_bytes;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(stage0 + kClStages * G::stage_bytes);
+  T* XT = reinterpret_cast<T*>(sm);                               // pixel frame (TMA destination: 128-byte aligned boxes)
+  T* S = reinterpret_cast<T*>(sm + G::x_bytes);
+  float2* Wsm = reinterpret_cast<float2*>(sm + G::x_bytes + G::s_bytes);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::x_bytes + G::s_bytes + G::w_bytes);
 
   const int tid = threadIdx.x;
+#ifdef WT_CL_TIMING
+  long long t_start = 0, t_first = 0, t_pass1 = 0;
+  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
+#endif
   // grid: x = band (column band fastest), y = channel group, z = slot group
   const int band = blockIdx.x;
   const int bx = band % a.nbx, by = band / a.nbx;
@@ -258,84 +324,112 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kClStages; ++s) cl_mbar_init(&bars[s], 1);
+    for (int s = 0; s <= G::NBOX; ++s) cl_mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-  constexpr unsigned kChunkBytes = (unsigned)(G::chunk_elems * sizeof(T));
-  if (tid == 0) {
+    // The whole pixel frame is requested at once: NBOX boxes per slot, one barrier per row range.
+    // Pixels outside the plane arrive as zeros (TMA out-of-bounds fill), which is both the odd-size
+    // padding of wtconv2d.py:49-51 and the 'same' padding of the convolutions.
 #pragma unroll
-    for (int s = 0; s < kClStages; ++s) {
-      if (s < G::NCHUNK) {
-        cl_mbar_expect_tx(&bars[s], kChunkBytes);
-        cl_tma_load4(stage0 + s * G::stage_bytes, &xmap, &bars[s], c0, X0, Y0 + 2 * s, n0);
-      }
+    for (int b = 0; b < G::NBOX; ++b) {
+      cl_mbar_expect_tx(&bars[b], (unsigned)(NS * G::box_bytes));
+#pragma unroll
+      for (int sl = 0; sl < NS; ++sl)
+        cl_tma_load4(XT + (size_t)sl * G::SLOT_X + (size_t)b * G::BOXR * XC * kClGroup, &xmap, &bars[b], c0, X0,
+                     Y0 + b * G::BOXR, n0 + sl);
     }
+    // tap sets of this stage, one bulk copy out of the channels-last parameter copy:
+    // [set][tap][16 channels] fp32; set 0 = base (taps, bias), 1..4 = sub-bands of the level
+    constexpr unsigned kSetBytes = (unsigned)(G::TAPS * kClGroup * sizeof(float));
+    const int nset = 1 + 4 * a.nlevels;
+    const float* src = a.packed + a.cl_off + ((size_t)blockIdx.y * nset + (BASE ? 0 : 1 + 4 * a.level)) * (G::TAPS * kClGroup);
+    const unsigned bytes = (BASE ? 5u : 4u) * kSetBytes;
+    cl_mbar_expect_tx(&bars[G::NBOX], bytes);
+    cl_bulk_load(reinterpret_cast<unsigned char*>(Wsm) + (BASE ? 0u : kSetBytes), src, bytes, &bars[G::NBOX]);
   }
-  // tap sets of this stage: [set][tap][channel] as fp32; set 0 = base (taps, bias), 1..4 = sub-bands
-  {
-    const int ts = a.tapset;
-    for (int i = tid; i < 5 * G::TAPS * kClGroup; i += G::NT) {
-      const int ch = i % kClGroup;
-      const int t = (i / kClGroup) % G::TAPS;
-      const int set = i / (kClGroup * G::TAPS);
-      float v = 0.f;
-      if (c0 + ch < a.C) {
-        const float* pc = a.packed + (size_t)(c0 + ch) * a.wstride;
-        if (set == 0) {
-          if (BASE) v = pc[t];                 // taps 0..K*K-1, bias in slot K*K
-        } else if (t < K * K) {
-          v = pc[ts * (1 + 4 * a.level + (set - 1)) + t];
-        }
-      }
-      reinterpret_cast<float*>(Wsm)[(set * G::TAPS + t) * kClGroup + ch] = v;
-    }
-  }
+  __syncthreads();     // barrier words initialised before anyone waits on them
 
-  // ---- pass 1: every chunk (two pixel rows) -> one row of the four sub-bands + the pixel copy
-  bool ok = true;
-#pragma unroll 1
-  for (int k = 0; k < G::NCHUNK; ++k) {
-    const int st = k % kClStages;
-    ok = cl_mbar_wait(&bars[st], (unsigned)((k / kClStages) & 1)) && ok;
-    const T* xs = reinterpret_cast<const T*>(stage0 + st * G::stage_bytes);
-    constexpr int ITEMS = NS * SC * kClLanes;
-    for (int it = tid; it < ITEMS; it += G::NT) {
-      const int cp = it & (kClLanes - 1);
-      const int blk = it >> 3;
-      const int f = blk % SC;
-      const int slot = blk / SC;
-      // staged box: [slot][row 0..1][column][16 channels]
-      const T* px = xs + (((size_t)slot * 2) * XC + 2 * f) * kClGroup + 2 * cp;
-      const float2 va = ClPair<T>::load(px), vb = ClPair<T>::load(px + kClGroup);
-      const float2 vc = ClPair<T>::load(px + XC * kClGroup), vd = ClPair<T>::load(px + XC * kClGroup + kClGroup);
-      const float2 pp = cl_add2(va, vb), qq = cl_sub2(va, vb), uu = cl_add2(vc, vd), vv = cl_sub2(vc, vd);
-      T* d = S + (size_t)slot * G::SLOT_S + ((size_t)k * SC + cl_swizzle<SL, NTX, 2, 1>(k, f)) * kClGroup + 2 * cp;
-      ClPair<T>::store(d, cl_add2(pp, uu));               // LL = a+b+c+d
-      ClPair<T>::store(d + G::SUB, cl_sub2(pp, uu));      // LH = a+b-c-d
-      ClPair<T>::store(d + 2 * G::SUB, cl_add2(qq, vv));  // HL = a-b+c-d
-      ClPair<T>::store(d + 3 * G::SUB, cl_sub2(qq, vv));  // HH = a-b-c+d
-      if (BASE) {
+  // ---- pass 1: pixel rows 2k, 2k+1 -> row k of the four sub-bands; for the base path the pixels
+  // are put back rotated (a permutation inside each 128-byte line, whose pixels belong to blocks
+  // handled by lanes of one warp).  A thread keeps the same blocks (slot, column, channel pair);
+  // the row loop is unrolled so that several independent rows are in flight per thread.
+  constexpr int ITEMS = NS * SC * kClLanes;
+  constexpr int NIT = (ITEMS + G::NT - 1) / G::NT;
+  static_assert(ITEMS % 32 == 0 && G::NT % 32 == 0, "blocks of one 128-byte line stay inside a warp");
+  int fcol[NIT];
+  T* sdst[NIT];
+  T* xsrc[NIT];
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-          const int fr = 2 * k + rr;                       // frame row of this pixel row
-          const int ra = fr - HS;                          // row of the pixel copy
-          if (ra >= 0 && ra < G::XRA) {
-            T* xr = XT + (size_t)slot * G::SLOT_X + (size_t)ra * XC * kClGroup + 2 * cp;
-            ClPair<T>::store(xr + cl_swizzle<SL, NTX, 3, 2>(fr, 2 * f) * kClGroup, rr ? vc : va);
-            ClPair<T>::store(xr + cl_swizzle<SL, NTX, 3, 2>(fr, 2 * f + 1) * kClGroup, rr ? vd : vb);
-          }
+  for (int j = 0; j < NIT; ++j) {
+    const int it = tid + j * G::NT;
+    const int cpj = it & (kClLanes - 1);
+    const int blk = it >> 3;
+    const int f = blk % SC;
+    const int slot = blk / SC;
+    fcol[j] = (it < ITEMS) ? f : -1;
+    sdst[j] = S + (size_t)slot * G::SLOT_S + 2 * cpj;
+    xsrc[j] = XT + (size_t)slot * G::SLOT_X + (size_t)(2 * f) * kClGroup + 2 * cpj;
+  }
+  bool ok = true;
+  constexpr int KU = (SR % 4 == 0) ? 4 : 2;
+#pragma unroll 1
+  for (int k0 = 0; k0 < SR; k0 += KU) {
+    for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + KU) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
+#ifdef WT_CL_TIMING
+    if (tid == 0 && k0 == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_first));
+#endif
+    raw_t px[KU][NIT][4];
+#pragma unroll
+    for (int kk = 0; kk < KU; ++kk)
+#pragma unroll
+      for (int j = 0; j < NIT; ++j) {
+        if (fcol[j] < 0) continue;
+        const T* p = xsrc[j] + (size_t)(2 * (k0 + kk)) * XC * kClGroup;
+        px[kk][j][0] = ClPair<T>::load_raw(p);
+        px[kk][j][1] = ClPair<T>::load_raw(p + kClGroup);
+        px[kk][j][2] = ClPair<T>::load_raw(p + XC * kClGroup);
+        px[kk][j][3] = ClPair<T>::load_raw(p + XC * kClGroup + kClGroup);
+      }
+    __syncwarp();                                     // every lane has read its pixels of these lines
+#pragma unroll
+    for (int kk = 0; kk < KU; ++kk) {
+      const int k = k0 + kk;
+      const int rrot = NTX * (k >> 1);
+      const bool keep = BASE && (2 * k >= HS) && (2 * k + 1 < G::XR - HS);   // rows the base convolution reads
+#pragma unroll
+      for (int j = 0; j < NIT; ++j) {
+        const int f = fcol[j];
+        if (f < 0) continue;
+        float2 sb[4];
+        cl_haar(ClPair<T>::widen(px[kk][j][0]), ClPair<T>::widen(px[kk][j][1]), ClPair<T>::widen(px[kk][j][2]),
+                ClPair<T>::widen(px[kk][j][3]), sb);
+        const int rot = ((f >> 2) + rrot) & (SL - 1);
+        const int fs = (f & ~(SL - 1)) + ((f + rot) & (SL - 1));
+        T* d = sdst[j] + ((size_t)k * SC + fs) * kClGroup;
+        ClPair<T>::store(d, sb[0]);
+        ClPair<T>::store(d + G::SUB, sb[1]);
+        ClPair<T>::store(d + 2 * G::SUB, sb[2]);
+        ClPair<T>::store(d + 3 * G::SUB, sb[3]);
+        if (keep) {
+          // pixel columns 2f, 2f+1 of frame rows 2k, 2k+1 belong to the same tile column and tile row
+          // as sub-band column f of row k, so they rotate by the same amount
+          T* p = xsrc[j] + (size_t)(2 * k) * XC * kClGroup;
+          const int g0 = 2 * f, g1 = 2 * f + 1;
+          const int d0 = ((g0 & ~(SL - 1)) + ((g0 + rot) & (SL - 1)) - g0) * kClGroup;
+          const int d1 = ((g1 & ~(SL - 1)) + ((g1 + rot) & (SL - 1)) - g1) * kClGroup;
+          ClPair<T>::store_raw(p + d0, px[kk][j][0]);
+          ClPair<T>::store_raw(p + kClGroup + d1, px[kk][j][1]);
+          ClPair<T>::store_raw(p + XC * kClGroup + d0, px[kk][j][2]);
+          ClPair<T>::store_raw(p + XC * kClGroup + kClGroup + d1, px[kk][j][3]);
         }
       }
     }
-    __syncthreads();
-    if (tid == 0 && k + kClStages < G::NCHUNK) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the chunk was read through the generic proxy
-      cl_mbar_expect_tx(&bars[st], kChunkBytes);
-      cl_tma_load4(stage0 + st * G::stage_bytes, &xmap, &bars[st], c0, X0, Y0 + 2 * (k + kClStages), n0);
-    }
   }
+  ok = cl_mbar_wait(&bars[G::NBOX], 0u) && ok;        // tap sets
   if (!ok && a.status) atomicExch(a.status, 1);
+  __syncthreads();
+#ifdef WT_CL_TIMING
+  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_pass1));
+#endif
 
   // ---- pass 2: per-thread tile
   const int cp = tid & (kClLanes - 1);
@@ -346,7 +440,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   const int n = n0 + slot;
   const int c = c0 + 2 * cp;
   const int gi = i0 + ty * kClRH, gj = j0 + tx * kClCW;      // first sub-band position of the tile
-  const bool live = (n < a.B) && (c < a.C) && (gi < a.Hh) && (gj < a.Wh);
+  const bool live = (q < NS * NTY * NTX) && (n < a.B) && (c < a.C) && (gi < a.Hh) && (gj < a.Wh);
   const bool pair = (c + 1 < a.C);
   if (!live) return;
 
@@ -374,6 +468,11 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
         }
       }
   }
+  float2 rin[kClRH][kClCW];          // scaled after the convolutions, so that the loads have time to land
+#pragma unroll
+  for (int i = 0; i < kClRH; ++i)
+#pragma unroll
+    for (int j = 0; j < kClCW; ++j) { rin[i][j] = acc[0][i][j]; acc[0][i][j] = make_float2(0.f, 0.f); }
   const int rot = (tx + NTX * ty) & (SL - 1);
   {
     const T* sbase = S + (size_t)slot * G::SLOT_S + ((size_t)(ty * kClRH) * SC + tx * kClCW) * kClGroup + 2 * cp;
@@ -389,13 +488,14 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     }
   }
 
-  // synthesis butterfly (un-normalised; the tap magnitudes are in the packed parameters)
+  // synthesis butterfly (its factor 1/2 is folded into the staged taps)
   float2 out[2 * kClRH][2 * kClCW];
+  const float2 rsc = make_float2(a.rin_scale, a.rin_scale);
 #pragma unroll
   for (int i = 0; i < kClRH; ++i)
 #pragma unroll
     for (int j = 0; j < kClCW; ++j) {
-      const float2 ll = acc[0][i][j], lh = acc[1][i][j], hl = acc[2][i][j], hh = acc[3][i][j];
+      const float2 ll = cl_fma2(rin[i][j], rsc, acc[0][i][j]), lh = acc[1][i][j], hl = acc[2][i][j], hh = acc[3][i][j];
       const float2 pp = cl_add2(ll, lh), qq = cl_sub2(ll, lh), uu = cl_add2(hl, hh), vv = cl_sub2(hl, hh);
       out[2 * i][2 * j] = cl_add2(pp, uu);
       out[2 * i][2 * j + 1] = cl_sub2(pp, uu);
@@ -408,30 +508,334 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     for (int i = 0; i < 2 * kClRH; ++i)
 #pragma unroll
       for (int j = 0; j < 2 * kClCW; ++j) out[i][j] = cl_add2(out[i][j], bias);
-    // window of the tile in the pixel copy: copy row 4*ty (= frame row 4*ty + HS), frame column 8*tx + HS
-    const T* xbase = XT + (size_t)slot * G::SLOT_X + ((size_t)(4 * ty) * XC + 8 * tx) * kClGroup + 2 * cp;
+    // window of the tile in the pixel frame: frame row 4*ty + HS, frame column 8*tx + HS
+    const T* xbase = XT + (size_t)slot * G::SLOT_X + ((size_t)(4 * ty + HS) * XC + 8 * tx) * kClGroup + 2 * cp;
     const T* px[SL];
 #pragma unroll
     for (int v = 0; v < SL; ++v) px[v] = xbase + ((v + rot) & (SL - 1)) * kClGroup;
     cl_base_conv<T, K, XC, SL, NTX>(out, px, Wsm + cp);
   }
   // store (cropped to the plane: wtconv2d.py:76)
-  TO* ob = static_cast<TO*>(a.out) + (size_t)n * a.os[0] + c;
   const int y0 = 2 * gi, x0 = 2 * gj;
+  TO* ob = static_cast<TO*>(a.out) + (size_t)n * a.os[0] + (size_t)y0 * a.os[2] + (size_t)x0 * a.os[3] + c;
+  if (a.out_vec && pair && y0 + 2 * kClRH <= a.H && x0 + 2 * kClCW <= a.W) {
 #pragma unroll
-  for (int i = 0; i < 2 * kClRH; ++i) {
-    if (y0 + i >= a.H) continue;
+    for (int i = 0; i < 2 * kClRH; ++i)
 #pragma unroll
-    for (int j = 0; j < 2 * kClCW; ++j) {
-      if (x0 + j >= a.W) continue;
-      TO* o = ob + (size_t)(y0 + i) * a.os[2] + (size_t)(x0 + j) * a.os[3];
-      if (a.out_vec && pair) ClPair<TO>::store(o, out[i][j]);
-      else {
-        o[0] = Elem<TO>::from_f(out[i][j].x);
-        if (pair) o[1] = Elem<TO>::from_f(out[i][j].y);
+      for (int j = 0; j < 2 * kClCW; ++j) ClPair<TO>::store(ob + (size_t)i * a.os[2] + (size_t)j * a.os[3], out[i][j]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2 * kClRH; ++i) {
+      if (y0 + i >= a.H) continue;
+#pragma unroll
+      for (int j = 0; j < 2 * kClCW; ++j) {
+        if (x0 + j >= a.W) continue;
+        TO* o = ob + (size_t)i * a.os[2] + (size_t)j * a.os[3];
+        if (a.out_vec && pair) ClPair<TO>::store(o, out[i][j]);
+        else {
+          o[0] = Elem<TO>::from_f(out[i][j].x);
+          if (pair) o[1] = Elem<TO>::from_f(out[i][j].y);
+        }
       }
     }
   }
+#ifdef WT_CL_TIMING
+  if (tid == 0 && a.status) {
+    long long t_end; unsigned smid;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_end));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    long long* d = reinterpret_cast<long long*>(a.status) + 8 * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+    d[0] = t_start; d[1] = t_first; d[2] = t_pass1; d[3] = t_end; d[4] = smid;
+  }
+#endif
+#endif
+}
+
+// ---------------------------------------------------------------------------
+// Sub-band pyramid kernel: the layer input -> the four sub-bands of the second level.
+//
+// One thread owns one channel pair of one 4 x 4 pixel block: the four 2 x 2 blocks give four
+// values of the first level's low-pass plane LL_1 (never stored) and their Haar step gives one
+// position of S_2 = {LL_2, LH_2, HL_2, HH_2}, written as (B, 4, h, w, C) planes in the input's
+// type at the reference's scale.  Channel pairs are the fastest thread index, so a warp reads
+// and writes 128 contiguous bytes per pixel.  Pixels outside the plane count as zeros
+// (wtconv2d.py:49-51).
+// ---------------------------------------------------------------------------
+struct ClPyramidArgs {
+  const void* x;
+  long long xs[4];      // strides in elements: n, c (= 1), h, w
+  int x_vec;            // 1: channel pairs may be loaded as one word
+  int B, C, H, W;
+  int h2, w2;           // size of the second level's sub-bands: ceil(ceil(H/2)/2), ...
+  void* s2;             // (B, 4, h2, w2, C)
+  long long total;      // B * h2 * w2 * ceil(C/2)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_constant__ ClPyramidArgs a) {
+#ifdef __CUDA_ARCH__
+  const int P = (a.C + 1) / 2;
+  const bool cpair = a.x_vec != 0;
+  for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < a.total; id += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(id % P);
+    long long t = id / P;
+    const int f = (int)(t % a.w2);
+    t /= a.w2;
+    const int k = (int)(t % a.h2);
+    const int n = (int)(t / a.h2);
+    const int c = 2 * p;
+    const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
+    const bool both = (c + 1 < a.C);
+    typename ClPair<T>::raw_t r[4][4];
+#pragma unroll
+    for (int yy = 0; yy < 4; ++yy)
+#pragma unroll
+      for (int xx = 0; xx < 4; ++xx)
+        r[yy][xx] = ClPair<T>::load_global(p0 + yy * a.xs[2] + xx * a.xs[3], 4 * k + yy < a.H && 4 * f + xx < a.W, cpair && both, both);
+    float2 l[2][2];
+#pragma unroll
+    for (int by = 0; by < 2; ++by)
+#pragma unroll
+      for (int bx = 0; bx < 2; ++bx) {
+        const float2 va = ClPair<T>::widen(r[2 * by][2 * bx]), vb = ClPair<T>::widen(r[2 * by][2 * bx + 1]);
+        const float2 vc = ClPair<T>::widen(r[2 * by + 1][2 * bx]), vd = ClPair<T>::widen(r[2 * by + 1][2 * bx + 1]);
+        l[by][bx] = __fmul2_rn(cl_add2(cl_add2(va, vb), cl_add2(vc, vd)), make_float2(0.5f, 0.5f));
+      }
+    float2 sb[4];
+    cl_haar(l[0][0], l[0][1], l[1][0], l[1][1], sb);
+    const size_t plane = (size_t)a.h2 * a.w2 * a.C;
+    T* d = static_cast<T*>(a.s2) + (size_t)n * 4 * plane + ((size_t)k * a.w2 + f) * a.C + c;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (both && (a.C & 1) == 0) ClPair<T>::store(d + s * plane, sb[s]);
+      else { d[s * plane] = Elem<T>::from_f(sb[s].x); if (both) d[s * plane + 1] = Elem<T>::from_f(sb[s].y); }
+    }
+  }
+#endif
+}
+
+// ---------------------------------------------------------------------------
+// Deep stage: every level from the second one down, whole planes on chip.
+//
+// A CTA owns NS plane slots (sample, 16-channel group).  The sub-bands of the second level
+// (from the pyramid kernel) arrive as one TMA box per sub-band, with the zero border the
+// convolutions need supplied by the out-of-bounds fill.  The analyses of the deeper levels,
+// the sub-band convolutions and the synthesis of every level then run out of shared memory,
+// deepest level first, and the reconstruction that the top level adds to its low-pass result
+// (wtconv2d.py:64-76) leaves as fp32 channels-last planes.
+//
+// On-chip level j = 1..nlev is layer level j+1.  S_j: frame of (h_j + 2*HS) x (w_j + 2*HS)
+// positions (rounded up to whole thread tiles) with a zero border, four sub-bands, kept in
+// the input's type at the reference's scale; R_j: fp32 reconstruction of level j,
+// h_{j-1} x w_{j-1}.
+// ---------------------------------------------------------------------------
+#ifdef __CUDA_ARCH__
+// Sub-band convolutions + synthesis of level j for every thread tile of the CTA's slots.
+template <typename T, int K, int RT, int CT>
+__device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsigned char* sm, const float2* Wsm,
+                                              int c0, int n0, int tid, int nthr) {
+  constexpr int TAPS = K * K + 1;
+  const int hj = a.h[j], wj = a.w[j], hp = a.h[j - 1], wp = a.w[j - 1];
+  const int tyn = cdiv(hj, RT), txn = cdiv(wj, CT);
+  const int ntile = a.ns * tyn * txn;
+  const int pitch = a.spitch[j], sub = a.ssub[j];
+  const T* Sj = reinterpret_cast<const T*>(sm + a.soff[j]);
+  const float* Rin = (j < a.nlev) ? reinterpret_cast<const float*>(sm + a.roff[j + 1]) : nullptr;
+  float* Rout = (j > 1) ? reinterpret_cast<float*>(sm + a.roff[j]) : nullptr;
+  const int cp = tid & (kClLanes - 1);
+  for (int q = tid >> 3; q < ntile; q += nthr >> 3) {
+    const int slot = q / (tyn * txn);
+    const int rem = q - slot * (tyn * txn);
+    const int ty = rem / txn, tx = rem - ty * txn;
+    const int gi = ty * RT, gj = tx * CT;
+    float2 acc[4][RT][CT];
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int jj = 0; jj < CT; ++jj) acc[s][i][jj] = make_float2(0.f, 0.f);
+    if (Rin) {
+      const float* rb = Rin + (size_t)slot * a.rslot[j + 1] + 2 * cp;
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int jj = 0; jj < CT; ++jj)
+          if (gi + i < hj && gj + jj < wj)
+            acc[0][i][jj] = __fmul2_rn(*reinterpret_cast<const float2*>(rb + ((gi + i) * wj + gj + jj) * kClGroup),
+                                       make_float2(0.5f, 0.5f));
+    }
+    const T* win = Sj + (size_t)slot * a.sslot[j] + ((size_t)gi * pitch + gj) * kClGroup + 2 * cp;
+#pragma unroll 1
+    for (int s = 0; s < 4; ++s) {
+      const float2* w = Wsm + s * TAPS * kClLanes + cp;
+      const T* ws = win + (size_t)s * sub;
+      float2 wr[K * K];
+#pragma unroll
+      for (int t = 0; t < K * K; ++t) wr[t] = w[t * kClLanes];
+      float2 y[RT][CT];
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int jj = 0; jj < CT; ++jj) y[i][jj] = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int iy = 0; iy < RT + K - 1; ++iy) {
+        float2 in[CT + K - 1];
+#pragma unroll
+        for (int c = 0; c < CT + K - 1; ++c) in[c] = ClPair<T>::load(ws + (iy * pitch + c) * kClGroup);
+#pragma unroll
+        for (int dy = 0; dy < K; ++dy) {
+          const int oy = iy - dy;
+          if (oy >= 0 && oy < RT) {
+#pragma unroll
+            for (int dx = 0; dx < K; ++dx)
+#pragma unroll
+              for (int ox = 0; ox < CT; ++ox) y[oy][ox] = cl_fma2(in[ox + dx], wr[dy * K + dx], y[oy][ox]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int jj = 0; jj < CT; ++jj) {
+          // the loop over s is kept rolled (four times less code); select the accumulator set by s
+          if (s == 0) acc[0][i][jj] = cl_add2(acc[0][i][jj], y[i][jj]);
+          else if (s == 1) acc[1][i][jj] = y[i][jj];
+          else if (s == 2) acc[2][i][jj] = y[i][jj];
+          else acc[3][i][jj] = y[i][jj];
+        }
+    }
+    const int n = n0 + slot;
+#pragma unroll
+    for (int i = 0; i < RT; ++i)
+#pragma unroll
+      for (int jj = 0; jj < CT; ++jj) {
+        const float2 ll = acc[0][i][jj], lh = acc[1][i][jj], hl = acc[2][i][jj], hh = acc[3][i][jj];
+        const float2 pp = cl_add2(ll, lh), qq = cl_sub2(ll, lh), uu = cl_add2(hl, hh), vv = cl_sub2(hl, hh);
+        const float2 o[2][2] = {{cl_add2(pp, uu), cl_sub2(pp, uu)}, {cl_add2(qq, vv), cl_sub2(qq, vv)}};
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+          for (int dx = 0; dx < 2; ++dx) {
+            const int yy = 2 * (gi + i) + dy, xx = 2 * (gj + jj) + dx;
+            if (yy < hp && xx < wp) {
+              if (Rout) {
+                *reinterpret_cast<float2*>(Rout + (size_t)slot * a.rslot[j] + (yy * wp + xx) * kClGroup + 2 * cp) = o[dy][dx];
+              } else if (n < a.B && c0 + 2 * cp < a.C) {
+                float* g = a.rout + (((size_t)n * hp + yy) * wp + xx) * a.C + c0 + 2 * cp;
+                if (c0 + 2 * cp + 1 < a.C && (a.C & 1) == 0) *reinterpret_cast<float2*>(g) = o[dy][dx];
+                else { g[0] = o[dy][dx].x; if (c0 + 2 * cp + 1 < a.C) g[1] = o[dy][dx].y; }
+              }
+            }
+          }
+      }
+  }
+}
+#endif
+
+template <typename T, int K>
+__global__ void __launch_bounds__(kClDeepThreads, 2)
+wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ ClDeepArgs a) {
+#ifdef __CUDA_ARCH__
+  constexpr int HS = K / 2;
+  constexpr int TAPS = K * K + 1;
+  constexpr unsigned kLevelBytes = 4u * TAPS * kClGroup * sizeof(float);
+  extern __shared__ unsigned char cl_smem_raw[];
+  unsigned char* sm = cl_smem_raw + ((128u - (cl_smem_addr(cl_smem_raw) & 127u)) & 127u);
+  unsigned char* wbuf = sm + a.woff;                 // two buffers of the four tap sets of a level
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + a.bar_off);   // two tap-set barriers, one for S_1
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int c0 = blockIdx.x * kClGroup;
+  const int n0 = blockIdx.y * a.ns;
+  const int nset = 1 + 4 * a.nlevels;
+  const float* wsrc = a.packed + a.cl_off + (size_t)blockIdx.x * nset * (TAPS * kClGroup);
+#ifdef WT_CL_TIMING
+  long long tt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[0]));
+#endif
+
+  if (tid == 0) {
+    for (int s = 0; s < 3; ++s) cl_mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // S_1 of every slot: one box per sub-band, starting HS positions outside the plane
+    cl_mbar_expect_tx(&bars[2], (unsigned)(a.ns * 4 * a.ssub[1] * (int)sizeof(T)));
+    for (int sl = 0; sl < a.ns; ++sl)
+      for (int sb = 0; sb < 4; ++sb)
+        cl_tma_load4(sm + a.soff[1] + ((size_t)sl * a.sslot[1] + (size_t)sb * a.ssub[1]) * sizeof(T), &xmap, &bars[2], c0,
+                     -HS, -HS, (n0 + sl) * 4 + sb);
+    // tap sets of the deepest level (layer level 1 + nlev, 0-based index nlev)
+    cl_mbar_expect_tx(&bars[0], kLevelBytes);
+    cl_bulk_load(wbuf, wsrc + (size_t)(1 + 4 * a.nlev) * (TAPS * kClGroup), kLevelBytes, &bars[0]);
+  }
+  // zero borders (and overhang) of the deeper frames (S_1 is filled whole by the TMA boxes)
+  for (int i = tid; i < a.zero_bytes / 16; i += nthr)
+    reinterpret_cast<uint4*>(sm + a.zero_off)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  bool ok = cl_mbar_wait(&bars[2], 0u);
+#ifdef WT_CL_TIMING
+  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[2]));
+#endif
+
+  // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j
+  for (int j = 2; j <= a.nlev; ++j) {
+    const T* Sp = reinterpret_cast<const T*>(sm + a.soff[j - 1]);
+    T* Sj = reinterpret_cast<T*>(sm + a.soff[j]);
+    const int hj = a.h[j], wj = a.w[j], pp_ = a.spitch[j - 1], pj = a.spitch[j], sub = a.ssub[j];
+    const int items = a.ns * hj * wj * kClLanes;
+    for (int it = tid; it < items; it += nthr) {
+      const int cp = it & (kClLanes - 1);
+      const int blk = it >> 3;
+      const int f = blk % wj;
+      const int r = (blk / wj) % hj;
+      const int slot = blk / (wj * hj);
+      // positions (2r, 2f) .. (2r+1, 2f+1) of the low-pass band; beyond the plane the frame holds zeros
+      const T* p = Sp + (size_t)slot * a.sslot[j - 1] + ((size_t)(2 * r + HS) * pp_ + 2 * f + HS) * kClGroup + 2 * cp;
+      const float2 va = ClPair<T>::load(p), vb = ClPair<T>::load(p + kClGroup);
+      const float2 vc = ClPair<T>::load(p + (size_t)pp_ * kClGroup), vd = ClPair<T>::load(p + (size_t)pp_ * kClGroup + kClGroup);
+      float2 sb[4];
+      cl_haar(va, vb, vc, vd, sb);
+      T* d = Sj + (size_t)slot * a.sslot[j] + ((size_t)(r + HS) * pj + f + HS) * kClGroup + 2 * cp;
+      ClPair<T>::store(d, sb[0]);
+      ClPair<T>::store(d + sub, sb[1]);
+      ClPair<T>::store(d + 2 * (size_t)sub, sb[2]);
+      ClPair<T>::store(d + 3 * (size_t)sub, sb[3]);
+    }
+    __syncthreads();
+  }
+
+#ifdef WT_CL_TIMING
+  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[3]));
+#endif
+  // ---- pass 3: convolutions + synthesis, deepest level first; the tap sets of the next level are
+  // copied while this one is computed
+  int cur = 0;
+  unsigned wphase[2] = {0u, 0u};
+  for (int j = a.nlev; j >= 1; --j) {
+    if (tid == 0 && j > 1) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the other buffer was read two levels ago
+      cl_mbar_expect_tx(&bars[1 - cur], kLevelBytes);
+      cl_bulk_load(wbuf + (size_t)(1 - cur) * kLevelBytes, wsrc + (size_t)(1 + 4 * (j - 1)) * (TAPS * kClGroup),
+                   kLevelBytes, &bars[1 - cur]);
+    }
+    ok = cl_mbar_wait(&bars[cur], wphase[cur]) && ok;
+    wphase[cur] ^= 1u;
+    const float2* Wsm = reinterpret_cast<const float2*>(wbuf + (size_t)cur * kLevelBytes);
+    if (a.h[j] * a.w[j] >= 32) cl_deep_level<T, K, kClRH, kClCW>(a, j, sm, Wsm, c0, n0, tid, nthr);
+    else cl_deep_level<T, K, 1, 2>(a, j, sm, Wsm, c0, n0, tid, nthr);
+    __syncthreads();
+    cur ^= 1;
+#ifdef WT_CL_TIMING
+    if (tid == 0 && j <= 4) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[3 + j]));   // tt[4..7]: end of levels 1..4
+#endif
+  }
+#ifdef WT_CL_TIMING
+  if (tid == 0 && a.status) {
+    long long* d = reinterpret_cast<long long*>(a.status) + 8 * (blockIdx.y * gridDim.x + blockIdx.x);
+    for (int i = 0; i < 8; ++i) d[i] = tt[i];
+  }
+#else
+  if (!ok && a.status) atomicExch(a.status, 1);
+#endif
 #endif
 }
 

@@ -222,11 +222,13 @@ inline long long plan_quad(QuadPlane& a, int B, int C, int K, int L, int q, int 
 
 struct Stage2d {
   // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg),
-  // 2: four-warp 14 x 14 level kernel (quad), 3: channels-last level stage (cl)
+  // 2: four-warp 14 x 14 level kernel (quad), 3: channels-last level stage (cl),
+  // 4: channels-last deep stage (deep), 5: channels-last sub-band pyramid of the layer input
   int kind = 0;
   RegPlane reg;
   QuadPlane quad;
   ClStage cl;
+  ClDeepArgs deep;
   Plan2d plan = Plan2d();
   long long xin_off;   // fp32 low-pass planes read as input (floats into scratch), -1: the layer input
   long long rin_off;   // reconstruction of the deeper levels read, -1: none
@@ -364,7 +366,7 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
   return true;
 }
 
-// The channels-last level stage (wt2d_cl.cuh) reads its input through a tensor map: channel
+// The channels-last kernels (wt2d_cl.cuh) read the layer input through a tensor map: channel
 // stride 1, every other stride and the base address multiples of 16 bytes.
 inline bool cl_stage_supported(const Layer2d& ly) {
   if (ly.K != 5 || ly.stride != 1 || ly.C < 8) return false;
@@ -376,11 +378,47 @@ inline bool cl_stage_supported(const Layer2d& ly) {
 }
 
 // Tile configuration of the channels-last level stage for a W-wide plane (see launch_shape)
+inline int& cl_tall_bands() { static int v = 0; return v; }
 inline int cl_config(int W) {
   if (W <= 8) return 4;
   if (W <= 16) return 3;
   if (W <= 32) return 2;
-  return 1;
+  return cl_tall_bands() ? 0 : 1;
+}
+
+// Description of a channels-last level stage.  level 0 with the base path finishes the layer
+// (input x, output y); a deeper level reads the low-pass plane of the level above from scratch
+// (dense channels-last, the layer's type) and writes an fp32 reconstruction.
+inline void plan_cl_level(ClStage& s, const Layer2d& ly, int level, int H, int W, bool rin_channels_last,
+                          float rin_scale) {
+  const bool final_stage = (level == 0);
+  s.B = ly.B; s.C = ly.C; s.H = H; s.W = W; s.K = ly.K;
+  s.level = level; s.has_base = final_stage ? 1 : 0;
+  s.config = cl_config(W);
+  s.nlevels = ly.L;
+  s.cl_off = cl_param_offset(ly.C, ly.K, ly.L);
+  const int Hh = (H + 1) / 2, Wh = (W + 1) / 2;
+  const long long dense[4] = {(long long)H * W * ly.C, 1, (long long)W * ly.C, ly.C};
+  for (int k = 0; k < 4; ++k) {
+    s.xs[k] = final_stage ? ly.xs[k] : dense[k];
+    s.os[k] = final_stage ? ly.ys[k] : dense[k];
+  }
+  if (rin_channels_last) {
+    s.rs[0] = (long long)Hh * Wh * ly.C; s.rs[1] = 1; s.rs[2] = (long long)Wh * ly.C; s.rs[3] = ly.C;
+    s.rin_vec = (ly.C % 2 == 0) ? 1 : 0;
+  } else {
+    s.rs[0] = (long long)ly.C * Hh * Wh; s.rs[1] = (long long)Hh * Wh; s.rs[2] = Wh; s.rs[3] = 1;
+    s.rin_vec = 0;
+  }
+  s.rin_scale = rin_scale;
+  s.x_vec = final_stage ? ((ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0)
+                        : ((ly.C % 2 == 0) ? 1 : 0);
+  if (final_stage) {
+    const int pair_bytes = 2 * ly.elem_size;
+    s.out_vec = (ly.y_align >= pair_bytes && (ly.ys[0] % 2) == 0 && (ly.ys[2] % 2) == 0 && (ly.ys[3] % 2) == 0) ? 1 : 0;
+  } else {
+    s.out_vec = (ly.C % 2 == 0) ? 1 : 0;
+  }
 }
 
 // Builds the launch chain of one layer.
@@ -397,6 +435,54 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // register-resident kernel (channels-last tensors, every remaining level), that kernel
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
   const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly);
+  cl_tall_bands() = (tune.cl == 3 && ly.elem_size == 2) ? 1 : 0;
+  // Channels-last tensors larger than 8 x 8: the sub-band pyramid kernel and a deep stage (whole
+  // planes on chip) for the levels below the top one, then the level stage of the top level with
+  // the base path.
+  if (use_cl && ly.L >= 1 && (ly.H > 8 || ly.W > 8) && tune.cl != 2) {
+    Stage2d deep;
+    bool deep_ok = true;
+    if (ly.L >= 2) {
+      deep_ok = false;
+      const int groups = cdiv(ly.C, kClGroup);
+      static const int cand[4] = {8, 4, 2, 1};
+      for (int i = 0; i < 4 && !deep_ok; ++i) {
+        const int ns = cand[i];
+        const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, ly.H, ly.W, ly.K, ly.L, ly.elem_size, ns);
+        if (bytes < 0) continue;
+        const bool enough = (long long)cdiv(ly.B, ns) * groups >= 296 || ns == 1;
+        if ((bytes <= kSmemTwoPerSm && enough) || (ns == 1 && bytes <= kSmemLimitBytes)) deep_ok = true;
+      }
+      // the tensor map of the sub-band planes needs 16-byte row strides
+      if ((ly.C * ly.elem_size) % 16 != 0) deep_ok = false;
+    }
+    if (deep_ok) {
+      if (ly.L >= 2) {
+        const long long n1 = ((long long)ly.B * Hl[1] * Wl[1] * ly.C + 3) / 4 * 4;    // floats of the level-1 reconstruction
+        const long long s2_elems = (long long)ly.B * 4 * Hl[2] * Wl[2] * ly.C;
+        Stage2d pyr;
+        pyr.kind = 5;
+        pyr.xin_off = -1; pyr.rin_off = -1; pyr.rout_off = n1;      // sub-bands of level 2, in the layer's type
+        pyr.smem_bytes = 0;
+        ch.stages.push_back(pyr);
+        deep.kind = 4;
+        deep.deep.cl_off = cl_param_offset(ly.C, ly.K, ly.L);
+        deep.xin_off = n1; deep.rin_off = -1; deep.rout_off = 0;
+        deep.smem_bytes = deep.deep.smem_bytes;
+        ch.stages.push_back(deep);
+        ch.scratch_floats = n1 + ((s2_elems * ly.elem_size + 3) / 4 + 3) / 4 * 4;
+      }
+      Stage2d st;
+      st.kind = 3;
+      plan_cl_level(st.cl, ly, 0, ly.H, ly.W, true, 0.5f);
+      st.smem_bytes = 0;
+      st.xin_off = -1;
+      st.rin_off = (ly.L >= 2) ? 0 : -1;
+      st.rout_off = -1;
+      ch.stages.push_back(st);
+      return ch;
+    }
+  }
   int qreg = -1;
   const bool untuned = !tune.force_tiled && !tune.tile_y && !tune.tile_x && !tune.tile_levels && !tune.group;
   if ((untuned || tune.regplane > 0) && tune.regplane >= 0 && ly.xs[1] == 1 && ly.C > 1) {
@@ -533,18 +619,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     const int H = Hl[c.first], W = Wl[c.first];
     if (use_cl && final_stage && c.nlev == 1) {
       st.kind = 3;
-      ClStage& s = st.cl;
-      s.B = ly.B; s.C = ly.C; s.H = H; s.W = W; s.K = ly.K;
-      s.level = 0; s.has_base = 1;
-      s.config = cl_config(W);
-      s.wstride = packed_channel_floats(ly.K, 2, ly.L);
-      s.tapset = tapset_floats(ly.K, 2);
-      const int Hh = Hl[1], Wh = Wl[1];
-      for (int k = 0; k < 4; ++k) { s.xs[k] = ly.xs[k]; s.os[k] = ly.ys[k]; }
-      s.rs[0] = (long long)ly.C * Hh * Wh; s.rs[1] = (long long)Hh * Wh; s.rs[2] = Wh; s.rs[3] = 1;
-      s.rin_vec = 0;
-      const int pair_bytes = 2 * ly.elem_size;
-      s.out_vec = (ly.y_align >= pair_bytes && (ly.ys[0] % 2) == 0 && (ly.ys[2] % 2) == 0 && (ly.ys[3] % 2) == 0) ? 1 : 0;
+      plan_cl_level(st.cl, ly, 0, ly.H, ly.W, false, 1.0f);
       st.smem_bytes = 0;
       st.xin_off = -1;
       st.rin_off = has_rin ? roff[i + 1] : -1;

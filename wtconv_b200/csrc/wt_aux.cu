@@ -10,6 +10,12 @@ __global__ void pack_params_kernel(PackArgs a, float* __restrict__ packed) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x)
     packed[i] = pack_value<P>(a, i);
+  if (a.cl_off > 0) {
+    const long long ncl = (long long)cdiv(a.C, 16) * (1 + a.subbands * a.L) * (a.taps + 1) * 16;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < ncl;
+         i += (long long)gridDim.x * blockDim.x)
+      packed[a.cl_off + i] = pack_value_cl<P>(a, i);
+  }
 }
 
 cudaError_t launch_pack(const PackArgs& a, int param_dtype, float* packed, cudaStream_t stream) {

@@ -25,7 +25,36 @@ struct PackArgs {
   const void* wavelet_scale[kMaxLevels];
   double gain[kMaxLevels];   // (analysis tap * synthesis tap)^(level+1)
   int adjoint;               // 1: reversed tap sets and no bias (block of the adjoint layer)
+  long long cl_off;          // 2-D: floats from the start of the block to its channels-last copy (0: none)
 };
+
+// Value of float `i` of the channels-last copy: [group][set][tap 0..taps][16 channels].  The
+// channels-last kernels keep every sub-band and reconstruction at the reference's scale (their
+// butterflies carry the factor 1/2 of a 2 x 2 Haar step themselves, which also keeps 16-bit
+// storage in range at deep levels), so the sub-band taps of level l are the per-channel values
+// times 4^(l+1) / 2: an exact power of two on top of the folded tap magnitudes.
+template <typename P> WT_HD float pack_value(const PackArgs& a, long long i);
+template <typename P>
+WT_HD float pack_value_cl(const PackArgs& a, long long i) {
+  const int ts1 = a.taps + 1;
+  const int nset = 1 + a.subbands * a.L;
+  const int ch = (int)(i % 16);
+  long long t = i / 16;
+  const int tap = (int)(t % ts1);
+  t /= ts1;
+  const int set = (int)(t % nset);
+  const int g = (int)(t / nset);
+  const int c = g * 16 + ch;
+  if (c >= a.C) return 0.f;
+  if (tap == a.taps && set != 0) return 0.f;
+  const int per_c = a.tapset * nset;
+  const float v = pack_value<P>(a, (long long)c * per_c + (long long)set * a.tapset + tap);
+  if (set == 0) return v;
+  const int l = (set - 1) / a.subbands;
+  float up = 2.f;                       // 4^(l+1) / 2
+  for (int k = 0; k < l; ++k) up *= 4.f;
+  return v * up;
+}
 
 // Value of packed float `i`.  Layout per channel c (ts = tap-set floats):
 //   [0, ts)                      base taps * base_scale[c]; slot K^d holds bias * base_scale[c]

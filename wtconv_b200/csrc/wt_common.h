@@ -59,6 +59,17 @@ WT_HD int packed_channel_floats(int K, int ndim, int L) {
   return tapset_floats(K, ndim) * (1 + sub * L);
 }
 
+// 2-D packed blocks carry a second copy of every tap set for the channels-last kernels, laid out
+// [channel group of 16][tap set][tap 0..K*K (last: bias slot)][16 channels] so that the sets one
+// CTA needs are a single contiguous run.  It starts cl_param_offset() floats into the block.
+WT_HD long long cl_param_offset(int C, int K, int L) {
+  const long long n = (long long)C * packed_channel_floats(K, 2, L);
+  return (n + 31) / 32 * 32;
+}
+WT_HD long long cl_param_floats(int C, int K, int L) {
+  return (long long)cdiv(C, 16) * (1 + 4 * L) * (K * K + 1) * 16;
+}
+
 // 16-byte asynchronous copy global -> shared (cp.async, no register staging).  Both addresses
 // must be 16-byte aligned.  async_wait_all() makes the calling thread's copies visible to it;
 // the CTA barrier that ends the phase publishes them to the other threads.
