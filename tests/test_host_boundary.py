@@ -33,20 +33,26 @@ def test_host_only_entry_points():
     L = _lib()
     lib = L.load()
     assert lib.wtconv_query(0) == 1 and lib.wtconv_query(1) == 7 and lib.wtconv_query(3) == 100
-    assert lib.wtconv_packed_param_floats(2, 96, 5, 5) == 96 * 28 * 21
+    # 2-D: per-channel block (28 floats per tap set, 1 + 4*5 sets) + channels-last copy (26 x 16 per set and group)
+    assert lib.wtconv_packed_param_floats(2, 96, 5, 5) == 96 * 28 * 21 + 6 * 21 * 26 * 16
     assert lib.wtconv_packed_param_floats(1, 64, 5, 4) == 64 * 8 * 9
     assert "odd" in L.status_string(-2)
     nbytes = ctypes.c_size_t(123)
     assert lib.wtconv2d_workspace_bytes(128, 192, 28, 28, 5, 4, 1, None, None, ctypes.byref(nbytes)) == 0
-    assert nbytes.value == 0                        # small planes: the whole cascade stays on chip
+    assert nbytes.value == 0                        # NCHW, small planes: the whole cascade stays on chip
+    cl = (ctypes.c_longlong * 4)(192 * 28 * 28, 1, 28 * 192, 192)
+    assert lib.wtconv2d_workspace_bytes(128, 192, 28, 28, 5, 4, 1, cl, cl, ctypes.byref(nbytes)) == 0
+    # channels-last: fp32 reconstruction of level 2 (14 x 14) + the four bf16 sub-bands of level 2 (7 x 7)
+    assert nbytes.value == 128 * 192 * (14 * 14 * 4 + 4 * 7 * 7 * 2)
     assert lib.wtconv2d_workspace_bytes(2, 256, 512, 512, 5, 5, 1, None, None, ctypes.byref(nbytes)) == 0
     assert 0 < nbytes.value <= 2 * 256 * 512 * 512 * 4 // 3
     assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, None, None, ctypes.byref(nbytes)) == -2
 
 
 def test_launch_chains_of_the_benchmark_shapes():
-    """Planner through the C ABI (host only): channels-last WTConvNeXt stage shapes end in the
-    register-level kernels, NCHW and other kernel sizes stay on the CTA-tile stages."""
+    """Planner through the C ABI (host only): large channels-last planes take the channels-last
+    chain (pyramid, deep stage, level stage), small ones the register-level kernels, NCHW and other
+    kernel sizes the CTA-tile stages."""
     L = _lib()
     lib = L.load()
 
@@ -56,9 +62,10 @@ def test_launch_chains_of_the_benchmark_shapes():
         assert lib.wtconv2d_launch_count(B, C, H, H, K, Lv, stride, code, st, st, ctypes.byref(n)) == 0
         return n.value
 
-    # bf16 channels-last: regplane | reduce, regplane, quad | + reduce, final | + deep
+    # bf16 channels-last: regplane | reduce, regplane, quad | pyramid, deep, level | the same
     assert [count(128, C, H, 5, Lv, 1, True) for C, H, Lv in
-            ((768, 7, 2), (384, 14, 3), (192, 28, 4), (96, 56, 5))] == [1, 3, 5, 6]
+            ((768, 7, 2), (384, 14, 3), (192, 28, 4), (96, 56, 5))] == [1, 3, 3, 3]
+    assert count(128, 96, 56, 5, 1, 1, True) == 1           # one level: the level stage alone
     assert count(128, 768, 7, 5, 2, 1, False) == 1          # NCHW: one whole-plane CTA-tile stage
     assert count(128, 96, 56, 5, 5, 1, False) == 1          # NCHW: the 56x56 pyramid still fits on chip
     assert count(2, 256, 512, 5, 5, 1, False) >= 4          # 512x512: reductions and a chain of tiled stages

@@ -49,7 +49,7 @@ cudaError_t make_map(CUtensorMap& map, const void* x, int B, int C, int H, int W
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MINB>
+template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MAXREG>
 cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* out, const float* packed, int* status,
                        cudaStream_t stream) {
   typedef ClGeo<T, K, NTY, NTX, NS> G;
@@ -76,7 +76,7 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   if (const char* e = getenv("WT_CL_DBG")) a.status = reinterpret_cast<int*>(strtoull(e, nullptr, 16));
 #endif
 
-  auto kern = wt2d_cl_level_kernel<T, TO, K, NTY, NTX, NS, BASE, MINB>;
+  auto kern = wt2d_cl_level_kernel<T, TO, K, NTY, NTX, NS, BASE, MAXREG>;
   constexpr size_t smem = G::smem_bytes;
   static bool done[kMaxDevices] = {false};
   cudaError_t e = allow_full_smem(kern, done);
@@ -91,11 +91,11 @@ template <typename T, typename TO, int K, bool BASE>
 cudaError_t launch_shape(const ClStage& s, const void* x, const float* rin, void* out, const float* packed,
                          int* status, cudaStream_t st) {
   switch (s.config) {
-    case 0: return launch_cfg<T, TO, K, 7, 7, 1, BASE, 1>(s, x, rin, out, packed, status, st);
-    case 1: return launch_cfg<T, TO, K, 4, 7, 1, BASE, 2>(s, x, rin, out, packed, status, st);
-    case 2: return launch_cfg<T, TO, K, 7, 4, 1, BASE, 2>(s, x, rin, out, packed, status, st);
-    case 3: return launch_cfg<T, TO, K, 4, 2, 2, BASE, 2>(s, x, rin, out, packed, status, st);
-    default: return launch_cfg<T, TO, K, 2, 1, 4, BASE, 2>(s, x, rin, out, packed, status, st);
+    case 0: return launch_cfg<T, TO, K, 7, 7, 1, BASE, 152>(s, x, rin, out, packed, status, st);
+    case 1: return launch_cfg<T, TO, K, 4, 7, 1, BASE, 128>(s, x, rin, out, packed, status, st);
+    case 2: return launch_cfg<T, TO, K, 7, 4, 1, BASE, 128>(s, x, rin, out, packed, status, st);
+    case 3: return launch_cfg<T, TO, K, 4, 2, 2, BASE, 168>(s, x, rin, out, packed, status, st);
+    default: return launch_cfg<T, TO, K, 2, 1, 4, BASE, 168>(s, x, rin, out, packed, status, st);
   }
 }
 

@@ -112,6 +112,13 @@ __device__ __forceinline__ void cl_haar(float2 a, float2 b, float2 c, float2 d, 
   sb[3] = cl_fma2(qq, h, __fmul2_rn(vv, mh));
 }
 
+// 8-byte shared-memory load that keeps its place among the other loads of this kind
+__device__ __forceinline__ float2 cl_lds2_ordered(const float* p) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cl_smem_addr(p)));
+  return v;
+}
+
 // plain bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`
 __device__ __forceinline__ void cl_bulk_load(void* dst, const void* src, unsigned bytes, void* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -190,28 +197,34 @@ template <> struct ClPair<__half> {
 };
 #endif
 
-// Compile-time geometry of one kernel configuration (T: type of the planes kept in shared memory)
+// Compile-time geometry of one kernel configuration (T: type of the input plane set).  The
+// sub-bands are kept as fp32 channel pairs, [row][sub-band][column][16 channels]; the pixel frame
+// (type T) lands at the start of the same region and is consumed, last rows first, just ahead of
+// the sub-band rows that overwrite it (see pass 1 of the kernel).
 template <typename T, int K, int NTY, int NTX, int NS>
 struct ClGeo {
   static constexpr int HS = K / 2;                          // halo of a K x K window
   static constexpr int SR = NTY * kClRH + 2 * HS;           // sub-band frame rows
   static constexpr int SC = ((NTX * kClCW + 2 * HS + 3) / 4) * 4;   // sub-band frame columns (whole rotation groups)
-  static constexpr int XR = 2 * SR, XC = 2 * SC;            // pixel frame delivered by the TMA chunks
+  static constexpr int XR = 2 * SR, XC = 2 * SC;            // pixel frame delivered by the TMA boxes
   static constexpr int NBOX = 4;                            // TMA boxes per slot, stacked along the rows
   static constexpr int BOXR = XR / NBOX;                    // pixel rows per box
   static_assert(XR % NBOX == 0, "the pixel frame is a whole number of boxes");
+  static constexpr int NIT1 = (NS * SC * kClLanes + (NTY * NTX * NS * kClLanes + 31) / 32 * 32 - 1) / ((NTY * NTX * NS * kClLanes + 31) / 32 * 32);   // blocks per thread and row
+  static constexpr int KU = (SR % 4 == 0 && NIT1 <= 2) ? 4 : 2;   // sub-band rows per batch of pass 1
+  static_assert(SR % KU == 0, "pass 1 works in whole batches");
   static constexpr int NT = (NTY * NTX * NS * kClLanes + 31) / 32 * 32;   // threads per CTA (whole warps)
   static constexpr int TAPS = K * K + 1;                    // staged floats per tap set and channel (last: bias slot)
-  static constexpr int PX = kClGroup;                       // elements of T per pixel
-  static constexpr int SL = 128 / (kClGroup * (int)sizeof(T));   // pixels per 128-byte line
-  static constexpr int SUB = SR * SC * PX;                  // elements per sub-band of a slot
-  static constexpr int SLOT_S = 4 * SUB;
-  static constexpr int SLOT_X = XR * XC * PX;
-  static constexpr size_t s_bytes = (size_t)NS * SLOT_S * sizeof(T);
-  static constexpr size_t x_bytes = (size_t)NS * SLOT_X * sizeof(T);
+  static constexpr int SL = 128 / (kClGroup * (int)sizeof(float));   // sub-band positions per 128-byte line
+  static constexpr int SUBS = SC * kClGroup;                // floats between the sub-bands of a row
+  static constexpr int ROWS = 4 * SUBS;                     // floats between rows
+  static constexpr int SLOT_S = SR * ROWS;                  // floats per slot
+  static constexpr size_t s_bytes = (size_t)NS * SLOT_S * sizeof(float);
+  static constexpr size_t frame_bytes = (size_t)XR * XC * kClGroup * sizeof(T);
+  static_assert(frame_bytes <= (size_t)SLOT_S * sizeof(float), "the pixel frame fits under its sub-bands");
+  static constexpr size_t box_bytes = (size_t)BOXR * XC * kClGroup * sizeof(T);
   static constexpr size_t w_bytes = (size_t)5 * TAPS * kClLanes * sizeof(float2);
-  static constexpr size_t box_bytes = (size_t)BOXR * XC * PX * sizeof(T);
-  static constexpr size_t smem_bytes = 128 /* alignment slack */ + s_bytes + x_bytes + w_bytes + 64 /* barriers */;
+  static constexpr size_t smem_bytes = 128 /* alignment slack */ + s_bytes + w_bytes + 64 /* barriers */;
 };
 
 // Rotation swizzle.  A pixel (16 channels) takes 128/SL bytes; the SL thread tiles served by one
@@ -229,9 +242,10 @@ WT_HD int cl_swizzle(int r, int f) {
 
 #ifdef __CUDA_ARCH__
 // acc[oy][ox] += sum_{dy,dx} w[dy][dx] * S(oy+dy, ox+dx) for one sub-band of the thread's window.
-// p[v]: base pointers of the window (channel pair included) for rotation class v.
-template <typename T, int K, int SC, int SL, int NTX>
-__device__ __forceinline__ void cl_subband_conv(float2 (&acc)[kClRH][kClCW], const T* const (&p)[SL],
+// p[v]: base pointers of the window (channel pair and sub-band included) for rotation class v;
+// RS: floats between rows.
+template <int K, int RS, int SL, int NTX>
+__device__ __forceinline__ void cl_subband_conv(float2 (&acc)[kClRH][kClCW], const float* const (&p)[SL],
                                                 const float2* __restrict__ w) {
   float2 wr[K * K];
 #pragma unroll
@@ -243,7 +257,7 @@ __device__ __forceinline__ void cl_subband_conv(float2 (&acc)[kClRH][kClCW], con
 #pragma unroll
     for (int c = 0; c < kClCW + K - 1; ++c) {
       const int v = ((c & (SL - 1)) + (c >> 2) + NTX * (iy >> 1)) & (SL - 1);
-      in[c] = ClPair<T>::load(p[v] + (iy * SC + (c & ~(SL - 1))) * kClGroup);
+      in[c] = *reinterpret_cast<const float2*>(p[v] + iy * RS + (c & ~(SL - 1)) * kClGroup);
     }
 #pragma unroll
     for (int dy = 0; dy < K; ++dy) {
@@ -258,56 +272,68 @@ __device__ __forceinline__ void cl_subband_conv(float2 (&acc)[kClRH][kClCW], con
   }
 }
 
-// Base convolution of the 4 x 8 pixel tile from the pixel copy; the window starts HS pixels
-// inside the frame, which the compile-time part of the rotation accounts for.
-template <typename T, int K, int XC, int SL, int NTX>
-__device__ __forceinline__ void cl_base_conv(float2 (&out)[2 * kClRH][2 * kClCW], const T* const (&p)[SL],
+// Base convolution of the 4 x 8 pixel tile.  The pixels are rebuilt from the four sub-bands, one
+// 2 x 2 block at a time (the Haar step is its own inverse), and every rebuilt pixel is added at
+// once to all the outputs it reaches, so no pixel rows are kept in registers.
+template <int K, int RS, int SUBS, int SL, int NTX>
+__device__ __forceinline__ void cl_base_conv(float2 (&out)[2 * kClRH][2 * kClCW], const float* const (&p)[SL],
                                              const float2* __restrict__ w) {
-  constexpr int HS = K / 2;
+  constexpr int HS = K / 2, BH = (HS + 1) / 2;
+  constexpr int OFF = 2 * BH - HS;                 // first rebuilt pixel row / column that is used
+  constexpr int NBR = kClRH + 2 * BH, NBC = kClCW + 2 * BH;   // blocks rebuilt
   float2 wr[K * K];
 #pragma unroll
-  for (int t = 0; t < K * K; ++t) wr[t] = w[t * kClLanes];
+  for (int t = 0; t < K * K; ++t) wr[t] = __fmul2_rn(w[t * kClLanes], make_float2(0.5f, 0.5f));   // 1/2 of the inverse step
 #pragma unroll
-  for (int iy = 0; iy < 2 * kClRH + K - 1; ++iy) {
-    asm volatile("" ::: "memory");
-    float2 in[2 * kClCW + K - 1];
+  for (int br = 0; br < NBR; ++br) {
 #pragma unroll
-    for (int c = 0; c < 2 * kClCW + K - 1; ++c) {
-      const int hc = HS + c, hd = HS + iy;
-      const int v = ((hc & (SL - 1)) + (hc >> 3) + NTX * (hd >> 2)) & (SL - 1);
-      in[c] = ClPair<T>::load(p[v] + (iy * XC + (hc & ~(SL - 1))) * kClGroup);
-    }
+    for (int bc = 0; bc < NBC; ++bc) {
+      const int fy = br + HS - BH, fx = bc + HS - BH;          // window position of this block
+      const int v = ((fx & (SL - 1)) + (fx >> 2) + NTX * (fy >> 1)) & (SL - 1);
+      const float* q = p[v] + fy * RS + (fx & ~(SL - 1)) * kClGroup;
+      // ordered loads: left to itself the compiler requests all the blocks up front and runs out of registers
+      const float2 ll = cl_lds2_ordered(q), lh = cl_lds2_ordered(q + SUBS);
+      const float2 hl = cl_lds2_ordered(q + 2 * SUBS), hh = cl_lds2_ordered(q + 3 * SUBS);
+      const float2 pp = cl_add2(ll, lh), qq = cl_sub2(ll, lh), uu = cl_add2(hl, hh), vv = cl_sub2(hl, hh);
+      const float2 px[2][2] = {{cl_add2(pp, uu), cl_sub2(pp, uu)}, {cl_add2(qq, vv), cl_sub2(qq, vv)}};
 #pragma unroll
-    for (int dy = 0; dy < K; ++dy) {
-      const int oy = iy - dy;
-      if (oy >= 0 && oy < 2 * kClRH) {
+      for (int a = 0; a < 2; ++a)
 #pragma unroll
-        for (int dx = 0; dx < K; ++dx)
+        for (int b = 0; b < 2; ++b) {
+          const int iy = 2 * br + a - OFF, ix = 2 * bc + b - OFF;   // position in the tile's input window
+          if (iy < 0 || iy >= 2 * kClRH + K - 1 || ix < 0 || ix >= 2 * kClCW + K - 1) continue;
 #pragma unroll
-          for (int ox = 0; ox < 2 * kClCW; ++ox) out[oy][ox] = cl_fma2(in[ox + dx], wr[dy * K + dx], out[oy][ox]);
-      }
+          for (int dy = 0; dy < K; ++dy) {
+            const int oy = iy - dy;
+            if (oy < 0 || oy >= 2 * kClRH) continue;
+#pragma unroll
+            for (int dx = 0; dx < K; ++dx) {
+              const int ox = ix - dx;
+              if (ox < 0 || ox >= 2 * kClCW) continue;
+              out[oy][ox] = cl_fma2(px[a][b], wr[dy * K + dx], out[oy][ox]);
+            }
+          }
+        }
     }
   }
 }
 #endif
 
-// T: type of the input plane set (and of the copies in shared memory); TO: type of the output (T
-// for the layer output, float for a reconstruction handed to the next shallower level); BASE: add
-// the base path.
-template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MINB>
-__global__ void __launch_bounds__((NTY * NTX * NS * kClLanes + 31) / 32 * 32, MINB)
+// T: type of the input plane set; TO: type of the output (T for the layer output, float for a
+// reconstruction handed to the next shallower level); BASE: add the base path.
+template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MAXREG>
+__global__ void __launch_bounds__((NTY * NTX * NS * kClLanes + 31) / 32 * 32) __maxnreg__(MAXREG)
 wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ ClArgs a) {
 #ifdef __CUDA_ARCH__
   typedef ClGeo<T, K, NTY, NTX, NS> G;
   typedef typename ClPair<T>::raw_t raw_t;
-  constexpr int SC = G::SC, SR = G::SR, HS = G::HS, SL = G::SL, XC = G::XC;
+  constexpr int SC = G::SC, SR = G::SR, HS = G::HS, SL = G::SL, XC = G::XC, KU = G::KU;
   static_assert(kClRH == 2 && kClCW == 4, "the swizzle assumes 2 x 4 thread tiles");
   extern __shared__ unsigned char cl_smem_raw[];
   unsigned char* sm = cl_smem_raw + ((128u - (cl_smem_addr(cl_smem_raw) & 127u)) & 127u);
-  T* XT = reinterpret_cast<T*>(sm);                               // pixel frame (TMA destination: 128-byte aligned boxes)
-  T* S = reinterpret_cast<T*>(sm + G::x_bytes);
-  float2* Wsm = reinterpret_cast<float2*>(sm + G::x_bytes + G::s_bytes);
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::x_bytes + G::s_bytes + G::w_bytes);
+  float* S = reinterpret_cast<float*>(sm);                          // sub-bands; the pixel frame lands on top of them
+  float2* Wsm = reinterpret_cast<float2*>(sm + G::s_bytes);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::s_bytes + G::w_bytes);
 
   const int tid = threadIdx.x;
 #ifdef WT_CL_TIMING
@@ -334,7 +360,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       cl_mbar_expect_tx(&bars[b], (unsigned)(NS * G::box_bytes));
 #pragma unroll
       for (int sl = 0; sl < NS; ++sl)
-        cl_tma_load4(XT + (size_t)sl * G::SLOT_X + (size_t)b * G::BOXR * XC * kClGroup, &xmap, &bars[b], c0, X0,
+        cl_tma_load4(sm + (size_t)sl * G::SLOT_S * sizeof(float) + (size_t)b * G::box_bytes, &xmap, &bars[b], c0, X0,
                      Y0 + b * G::BOXR, n0 + sl);
     }
     // tap sets of this stage, one bulk copy out of the channels-last parameter copy:
@@ -348,16 +374,17 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   }
   __syncthreads();     // barrier words initialised before anyone waits on them
 
-  // ---- pass 1: pixel rows 2k, 2k+1 -> row k of the four sub-bands; for the base path the pixels
-  // are put back rotated (a permutation inside each 128-byte line, whose pixels belong to blocks
-  // handled by lanes of one warp).  A thread keeps the same blocks (slot, column, channel pair);
-  // the row loop is unrolled so that several independent rows are in flight per thread.
+  // ---- pass 1: pixel rows 2k, 2k+1 of the frame -> row k of the four sub-bands (one Haar step at
+  // the reference's scale).  Batches of KU rows, last rows first: a batch is read into registers,
+  // the CTA meets, and only then are its sub-band rows written -- they cover frame rows of this
+  // and of earlier batches only (a sub-band row takes at least the bytes of its two pixel rows and
+  // both arrays start at the same address).  A thread keeps the same blocks (slot, column,
+  // channel pair) in every batch.
   constexpr int ITEMS = NS * SC * kClLanes;
   constexpr int NIT = (ITEMS + G::NT - 1) / G::NT;
-  static_assert(ITEMS % 32 == 0 && G::NT % 32 == 0, "blocks of one 128-byte line stay inside a warp");
   int fcol[NIT];
-  T* sdst[NIT];
-  T* xsrc[NIT];
+  float* sdst[NIT];
+  const T* fsrc[NIT];
 #pragma unroll
   for (int j = 0; j < NIT; ++j) {
     const int it = tid + j * G::NT;
@@ -367,15 +394,14 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     const int slot = blk / SC;
     fcol[j] = (it < ITEMS) ? f : -1;
     sdst[j] = S + (size_t)slot * G::SLOT_S + 2 * cpj;
-    xsrc[j] = XT + (size_t)slot * G::SLOT_X + (size_t)(2 * f) * kClGroup + 2 * cpj;
+    fsrc[j] = reinterpret_cast<const T*>(S + (size_t)slot * G::SLOT_S) + (size_t)(2 * f) * kClGroup + 2 * cpj;
   }
   bool ok = true;
-  constexpr int KU = (SR % 4 == 0) ? 4 : 2;
 #pragma unroll 1
-  for (int k0 = 0; k0 < SR; k0 += KU) {
+  for (int k0 = SR - KU; k0 >= 0; k0 -= KU) {
     for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + KU) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
 #ifdef WT_CL_TIMING
-    if (tid == 0 && k0 == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_first));
+    if (tid == 0 && k0 == SR - KU) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_first));
 #endif
     raw_t px[KU][NIT][4];
 #pragma unroll
@@ -383,18 +409,17 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 #pragma unroll
       for (int j = 0; j < NIT; ++j) {
         if (fcol[j] < 0) continue;
-        const T* p = xsrc[j] + (size_t)(2 * (k0 + kk)) * XC * kClGroup;
+        const T* p = fsrc[j] + (size_t)(2 * (k0 + kk)) * XC * kClGroup;
         px[kk][j][0] = ClPair<T>::load_raw(p);
         px[kk][j][1] = ClPair<T>::load_raw(p + kClGroup);
         px[kk][j][2] = ClPair<T>::load_raw(p + XC * kClGroup);
         px[kk][j][3] = ClPair<T>::load_raw(p + XC * kClGroup + kClGroup);
       }
-    __syncwarp();                                     // every lane has read its pixels of these lines
+    __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < KU; ++kk) {
       const int k = k0 + kk;
       const int rrot = NTX * (k >> 1);
-      const bool keep = BASE && (2 * k >= HS) && (2 * k + 1 < G::XR - HS);   // rows the base convolution reads
 #pragma unroll
       for (int j = 0; j < NIT; ++j) {
         const int f = fcol[j];
@@ -404,23 +429,9 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
                 ClPair<T>::widen(px[kk][j][3]), sb);
         const int rot = ((f >> 2) + rrot) & (SL - 1);
         const int fs = (f & ~(SL - 1)) + ((f + rot) & (SL - 1));
-        T* d = sdst[j] + ((size_t)k * SC + fs) * kClGroup;
-        ClPair<T>::store(d, sb[0]);
-        ClPair<T>::store(d + G::SUB, sb[1]);
-        ClPair<T>::store(d + 2 * G::SUB, sb[2]);
-        ClPair<T>::store(d + 3 * G::SUB, sb[3]);
-        if (keep) {
-          // pixel columns 2f, 2f+1 of frame rows 2k, 2k+1 belong to the same tile column and tile row
-          // as sub-band column f of row k, so they rotate by the same amount
-          T* p = xsrc[j] + (size_t)(2 * k) * XC * kClGroup;
-          const int g0 = 2 * f, g1 = 2 * f + 1;
-          const int d0 = ((g0 & ~(SL - 1)) + ((g0 + rot) & (SL - 1)) - g0) * kClGroup;
-          const int d1 = ((g1 & ~(SL - 1)) + ((g1 + rot) & (SL - 1)) - g1) * kClGroup;
-          ClPair<T>::store_raw(p + d0, px[kk][j][0]);
-          ClPair<T>::store_raw(p + kClGroup + d1, px[kk][j][1]);
-          ClPair<T>::store_raw(p + XC * kClGroup + d0, px[kk][j][2]);
-          ClPair<T>::store_raw(p + XC * kClGroup + kClGroup + d1, px[kk][j][3]);
-        }
+        float* d = sdst[j] + (size_t)k * G::ROWS + fs * kClGroup;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) *reinterpret_cast<float2*>(d + s * G::SUBS) = sb[s];
       }
     }
   }
@@ -444,14 +455,12 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   const bool pair = (c + 1 < a.C);
   if (!live) return;
 
-  float2 acc[4][kClRH][kClCW];
+  // deeper reconstruction (wtconv2d.py:71), requested before the convolutions
+  float2 rin[kClRH][kClCW];
 #pragma unroll
-  for (int s = 0; s < 4; ++s)
+  for (int i = 0; i < kClRH; ++i)
 #pragma unroll
-    for (int i = 0; i < kClRH; ++i)
-#pragma unroll
-      for (int j = 0; j < kClCW; ++j) acc[s][i][j] = make_float2(0.f, 0.f);
-  // deeper reconstruction -> low-pass accumulators (wtconv2d.py:71), requested before the convolutions
+    for (int j = 0; j < kClCW; ++j) rin[i][j] = make_float2(0.f, 0.f);
   if (a.rin) {
     const float* rb = a.rin + (size_t)n * a.rs[0] + (size_t)c * a.rs[1];
 #pragma unroll
@@ -460,32 +469,33 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       for (int j = 0; j < kClCW; ++j) {
         if (gi + i < a.Hh && gj + j < a.Wh) {
           const float* rp = rb + (size_t)(gi + i) * a.rs[2] + (size_t)(gj + j) * a.rs[3];
-          if (a.rin_vec) acc[0][i][j] = __ldg(reinterpret_cast<const float2*>(rp));
+          if (a.rin_vec) rin[i][j] = __ldg(reinterpret_cast<const float2*>(rp));
           else {
-            acc[0][i][j].x = __ldg(rp);
-            if (pair) acc[0][i][j].y = __ldg(rp + a.rs[1]);
+            rin[i][j].x = __ldg(rp);
+            if (pair) rin[i][j].y = __ldg(rp + a.rs[1]);
           }
         }
       }
   }
-  float2 rin[kClRH][kClCW];          // scaled after the convolutions, so that the loads have time to land
+  float2 acc[4][kClRH][kClCW];
 #pragma unroll
-  for (int i = 0; i < kClRH; ++i)
+  for (int s = 0; s < 4; ++s)
 #pragma unroll
-    for (int j = 0; j < kClCW; ++j) { rin[i][j] = acc[0][i][j]; acc[0][i][j] = make_float2(0.f, 0.f); }
+    for (int i = 0; i < kClRH; ++i)
+#pragma unroll
+      for (int j = 0; j < kClCW; ++j) acc[s][i][j] = make_float2(0.f, 0.f);
+  // window of the tile: sub-band frame row 2*ty, column 4*tx; rotation classes relative to the tile's own
   const int rot = (tx + NTX * ty) & (SL - 1);
-  {
-    const T* sbase = S + (size_t)slot * G::SLOT_S + ((size_t)(ty * kClRH) * SC + tx * kClCW) * kClGroup + 2 * cp;
-    const T* ps[SL];
+  const float* sbase = S + (size_t)slot * G::SLOT_S + (size_t)(ty * kClRH) * G::ROWS + (tx * kClCW) * kClGroup + 2 * cp;
+  const float* ps[SL];
 #pragma unroll
-    for (int v = 0; v < SL; ++v) ps[v] = sbase + ((v + rot) & (SL - 1)) * kClGroup;
+  for (int v = 0; v < SL; ++v) ps[v] = sbase + ((v + rot) & (SL - 1)) * kClGroup;
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const T* pss[SL];
+  for (int s = 0; s < 4; ++s) {
+    const float* pss[SL];
 #pragma unroll
-      for (int v = 0; v < SL; ++v) pss[v] = ps[v] + s * G::SUB;
-      cl_subband_conv<T, K, SC, SL, NTX>(acc[s], pss, Wsm + (1 + s) * G::TAPS * kClLanes + cp);
-    }
+    for (int v = 0; v < SL; ++v) pss[v] = ps[v] + s * G::SUBS;
+    cl_subband_conv<K, G::ROWS, SL, NTX>(acc[s], pss, Wsm + (1 + s) * G::TAPS * kClLanes + cp);
   }
 
   // synthesis butterfly (its factor 1/2 is folded into the staged taps)
@@ -508,12 +518,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     for (int i = 0; i < 2 * kClRH; ++i)
 #pragma unroll
       for (int j = 0; j < 2 * kClCW; ++j) out[i][j] = cl_add2(out[i][j], bias);
-    // window of the tile in the pixel frame: frame row 4*ty + HS, frame column 8*tx + HS
-    const T* xbase = XT + (size_t)slot * G::SLOT_X + ((size_t)(4 * ty + HS) * XC + 8 * tx) * kClGroup + 2 * cp;
-    const T* px[SL];
-#pragma unroll
-    for (int v = 0; v < SL; ++v) px[v] = xbase + ((v + rot) & (SL - 1)) * kClGroup;
-    cl_base_conv<T, K, XC, SL, NTX>(out, px, Wsm + cp);
+    cl_base_conv<K, G::ROWS, G::SUBS, SL, NTX>(out, ps, Wsm + cp);
   }
   // store (cropped to the plane: wtconv2d.py:76)
   const int y0 = 2 * gi, x0 = 2 * gj;
@@ -734,7 +739,7 @@ __device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsign
 #endif
 
 template <typename T, int K>
-__global__ void __launch_bounds__(kClDeepThreads, 2)
+__global__ void __launch_bounds__(kClDeepThreads, 1)
 wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ ClDeepArgs a) {
 #ifdef __CUDA_ARCH__
   constexpr int HS = K / 2;

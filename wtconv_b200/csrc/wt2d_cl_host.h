@@ -10,7 +10,7 @@ constexpr int kClGroup = 16;          // channels per plane slot
 constexpr int kClLanes = 8;           // lanes (channel pairs) per thread tile
 constexpr int kClRH = 2, kClCW = 4;   // sub-band positions per thread tile
 constexpr int kClDeepMaxLev = 8;      // levels the deep stage can hold on chip
-constexpr int kClDeepThreads = 256;
+constexpr int kClDeepThreads = 512;
 
 struct ClStage {
   int B, C, H, W;        // input plane set of the level (channels-last)

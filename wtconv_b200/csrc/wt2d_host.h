@@ -436,22 +436,27 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
   const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly);
   cl_tall_bands() = (tune.cl == 3 && ly.elem_size == 2) ? 1 : 0;
-  // Channels-last tensors larger than 8 x 8: the sub-band pyramid kernel and a deep stage (whole
+  // Channels-last tensors larger than 16 x 16 (smaller planes are faster in the register-level
+  // kernels below): the sub-band pyramid kernel and a deep stage (whole
   // planes on chip) for the levels below the top one, then the level stage of the top level with
   // the base path.
-  if (use_cl && ly.L >= 1 && (ly.H > 8 || ly.W > 8) && tune.cl != 2) {
+  if (use_cl && ly.L >= 1 && (ly.H > 16 || ly.W > 16) && tune.cl != 2) {
     Stage2d deep;
     bool deep_ok = true;
     if (ly.L >= 2) {
       deep_ok = false;
       const int groups = cdiv(ly.C, kClGroup);
-      static const int cand[4] = {8, 4, 2, 1};
-      for (int i = 0; i < 4 && !deep_ok; ++i) {
+      // one CTA of sixteen warps per SM: as many slots as keep its threads busy at the largest
+      // level (28 thread tiles of eight lanes fill seven warps) and leave two waves of CTAs
+      static const int cand[5] = {16, 8, 4, 2, 1};
+      for (int i = 0; i < 5 && !deep_ok; ++i) {
         const int ns = cand[i];
         const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, ly.H, ly.W, ly.K, ly.L, ly.elem_size, ns);
-        if (bytes < 0) continue;
-        const bool enough = (long long)cdiv(ly.B, ns) * groups >= 296 || ns == 1;
-        if ((bytes <= kSmemTwoPerSm && enough) || (ns == 1 && bytes <= kSmemLimitBytes)) deep_ok = true;
+        if (bytes < 0 || bytes > kSmemLimitBytes) continue;
+        const int tiles = cdiv(deep.deep.h[1], kClRH) * cdiv(deep.deep.w[1], kClCW);
+        const bool enough = (long long)cdiv(ly.B, ns) * groups >= 2 * 148 || ns == 1;
+        const bool useful = (ns == 1) || (long long)(ns / 2) * tiles * kClLanes < kClDeepThreads;
+        if (enough && useful) deep_ok = true;
       }
       // the tensor map of the sub-band planes needs 16-byte row strides
       if ((ly.C * ly.elem_size) % 16 != 0) deep_ok = false;
