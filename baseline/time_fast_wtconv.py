@@ -9,12 +9,13 @@ checkout is readable; the build needs nvcc but no GPU)::
 
     python baseline/time_fast_wtconv.py --install <path of the reference checkout>
 
-which copies ``fast_wtconv/`` to ``baseline/_ref/src`` (ignored by git) and JIT-builds its extension
-for sm_100 into ``baseline/_ref/torch_ext``.  Then, on a B200::
+which copies ``fast_wtconv/`` and ``wtconv/`` to ``baseline/_ref/src`` (ignored by git) and JIT-builds the
+CUDA extension for sm_100 into ``baseline/_ref/torch_ext``.  Then, on a B200::
 
     python baseline/time_fast_wtconv.py
 
-Not used by bench.py: the reference arm there is the CPU implementation.
+bench.py uses the same copies: ``wtconv/`` for its CPU reference arm and ``fast_wtconv/`` for the
+secondary GPU comparison in its JSON line.
 """
 import argparse
 import os
@@ -33,10 +34,13 @@ STAGES = [(96, 56, 5), (192, 28, 4), (384, 14, 3), (768, 7, 2)]   # (C, H=W, wt_
 
 
 def install(checkout):
-    dst = os.path.join(REF, "src", "fast_wtconv")
-    if os.path.isdir(dst):
-        shutil.rmtree(dst)
-    shutil.copytree(os.path.join(checkout, "fast_wtconv"), dst)
+    # fast_wtconv: the reference's CUDA backend (GPU comparator); wtconv: its pure-PyTorch layer, which
+    # bench.py --impl reference runs unchanged on the host cores
+    for pkg in ("fast_wtconv", "wtconv"):
+        dst = os.path.join(REF, "src", pkg)
+        if os.path.isdir(dst):
+            shutil.rmtree(dst)
+        shutil.copytree(os.path.join(checkout, pkg), dst)
     from fast_wtconv.cuda_haar import haar_cuda
     print("built", haar_cuda._get_module())
 

@@ -38,6 +38,7 @@ extern "C" {
 #define WTCONV_ERR_TOO_LARGE (-6)      /* a dimension overflows the 32-bit index plan       */
 #define WTCONV_ERR_NO_DEVICE (-7)      /* no usable CUDA device / not an sm_100 device      */
 #define WTCONV_ERR_SCRATCH_LIMIT (-8)  /* problem needs more than WTCONV_STATIC_SCRATCH_BYTES */
+#define WTCONV_ERR_DEVICE_WAIT (-9)    /* a kernel gave up a bounded wait (wtconv_device_status) */
 
 /* size of the scratch array built into the library for wtconv2d_forward_noalloc */
 #define WTCONV_STATIC_SCRATCH_BYTES (16u << 20)
@@ -55,6 +56,15 @@ int wtconv_query(int what);
 /* Human-readable text for a status returned by any entry point (static string).
  * Counterpart of the TORCH_CHECK messages of fast_wtconv/cuda_haar/fused_haar_conv.cu:399-417. */
 const char* wtconv_status_string(int status);
+
+/* Health check of the kernels that are fed by asynchronous bulk copies (TMA).  They poll the
+ * completion barrier of a copy a bounded number of times; should a copy never complete, the
+ * kernel sets a status word on the device and runs to its end instead of spinning for ever.
+ * This call waits for `stream` (cudaStreamSynchronize), reads the word of the current device
+ * and clears it.  Returns WTCONV_OK, or WTCONV_ERR_DEVICE_WAIT when some launch since the last
+ * check gave up a wait (its output is then invalid), or a cudaError_t.  No counterpart in the
+ * reference, whose kernels use no asynchronous copies. */
+int wtconv_device_status(void* stream);
 
 /* Number of floats of the packed parameter block for one layer.
  * ndim is 2 (WTConv2d) or 1 (WTConv1d). */
@@ -99,7 +109,8 @@ int wtconv_pack_params(int ndim, int C, int K, int L, int param_dtype,
  * gradient of the output gives the gradient of the input -- what autograd
  * computes for wtconv/wtconv2d.py:38-87 and what the reference CUDA backend
  * computes in fused_haar_conv_scale_bwd (fast_wtconv/cuda_haar/
- * fused_haar_conv.cu:148-234).  Parameter gradients are not provided.
+ * fused_haar_conv.cu:148-234).  Parameter gradients: wtconv2d_weight_grad_stats and
+ * wtconv_param_grads below.
  */
 int wtconv_pack_params_adjoint(int ndim, int C, int K, int L, int param_dtype,
                        double ana_tap, double syn_tap,
@@ -158,7 +169,10 @@ int wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x_pyr
  * small planes; larger planes hand the reconstruction of their deep levels --
  * a quarter-resolution fp32 plane set or smaller -- from one launch to the next
  * through scratch).  x_strides / y_strides as for wtconv2d_forward (NULL =
- * NCHW-contiguous); the answer does not depend on pointer alignment.
+ * NCHW-contiguous).  The launch chain also depends on whether the tensors start
+ * on 16-byte boundaries (the tensor maps of the TMA-fed kernels need that); the
+ * size reported covers both cases, so it is enough for any pointers with these
+ * strides.
  * The reference has no counterpart: its intermediates are torch allocations
  * inside wtconv/wtconv2d.py:46-78.
  */
@@ -211,14 +225,16 @@ int wtconv2d_forward(const void* x, void* y, const float* packed,
  * memory budget is frozen after start-up.
  *
  *   - Problems whose scratch need exceeds WTCONV_STATIC_SCRATCH_BYTES are
- *     rejected with WTCONV_ERR_SCRATCH_LIMIT before anything is launched (for
- *     example bf16 channels-last 56x56 planes with 5 levels need B*C*3136 bytes:
- *     up to B*C = 5349 planes fit).  Problems that need no scratch always pass.
+ *     rejected with WTCONV_ERR_SCRATCH_LIMIT before anything is launched; the
+ *     check plans with the pointers and strides of this very call (for example
+ *     bf16 channels-last 56x56 planes with 5 levels need B*C*4704 bytes: up to
+ *     B*C = 3566 planes fit).  Problems that need no scratch always pass.
  *   - Every GPU whose context loads the library holds the array until the
  *     process exits.
- *   - The first call on a device looks up the array's device address (one
- *     cudaGetSymbolAddress with that device current).  Make that first call
- *     before starting any stream capture.
+ *   - Every call looks up the array's address on the current device (one
+ *     cudaGetSymbolAddress, a host-side table lookup once the kernels are
+ *     loaded).  Make one call per device before starting any stream capture,
+ *     so that loading the kernels does not fall into the capture.
  *   - All calls on a device share the one array, which keeps whatever the last
  *     call left in it.  The kernels overwrite every scratch plane they later
  *     read, so nothing has to be cleared between calls; but two calls that can
@@ -237,6 +253,13 @@ int wtconv2d_forward_noalloc(const void* x, void* y, const float* packed,
  *   x (B,C,N) with 3 element strides (n,c,t); y (B,C,floor(N/stride)) --
  *   stride>1 is a true average pool of `stride` samples (wtconv1d.py:34).
  * The 1-D cascade is always fused on chip; no scratch memory is used.
+ * Limits of this build, narrower than the 2-D ones: wt_levels <= 8
+ * (WTCONV_ERR_BAD_LEVELS beyond); B <= 65535, C*N < 2^31 and at most 65535
+ * channel groups (WTCONV_ERR_TOO_LARGE); a signal tile must hold a multiple of
+ * 2^wt_levels * 8 * stride samples, so deep cascades combined with a large
+ * pooling stride on long signals (for example wt_levels 8, stride >= 6,
+ * N > 12000) exceed the shared memory of an SM and are rejected with
+ * WTCONV_ERR_TOO_LARGE as well.
  */
 int wtconv1d_forward(const void* x, void* y, const float* packed,
                      int B, int C, int N, int K, int L, int stride, int dtype,

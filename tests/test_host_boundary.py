@@ -43,7 +43,11 @@ def test_host_only_entry_points():
     cl = (ctypes.c_longlong * 4)(192 * 28 * 28, 1, 28 * 192, 192)
     assert lib.wtconv2d_workspace_bytes(128, 192, 28, 28, 5, 4, 1, cl, cl, ctypes.byref(nbytes)) == 0
     # channels-last: fp32 reconstruction of level 2 (14 x 14) + the four bf16 sub-bands of level 2 (7 x 7)
-    assert nbytes.value == 128 * 192 * (14 * 14 * 4 + 4 * 7 * 7 * 2)
+    # when the tensors start on 16-byte boundaries; the chain of unaligned tensors (low-pass planes and
+    # reconstructions of levels 1 and 2 in fp32) needs more, and the larger figure is reported
+    aligned = 128 * 192 * (14 * 14 * 4 + 4 * 7 * 7 * 2)
+    unaligned = 128 * 192 * (2 * 14 * 14 + 2 * 7 * 7) * 4
+    assert nbytes.value == max(aligned, unaligned)
     assert lib.wtconv2d_workspace_bytes(2, 256, 512, 512, 5, 5, 1, None, None, ctypes.byref(nbytes)) == 0
     assert 0 < nbytes.value <= 2 * 256 * 512 * 512 * 4 // 3
     assert lib.wtconv2d_workspace_bytes(2, 8, 16, 16, 4, 5, 1, None, None, ctypes.byref(nbytes)) == -2

@@ -24,6 +24,7 @@ _VP, _I, _LLP = ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_longlong)
 SYMBOLS = {
     "wtconv_query": (_I, [_I]),
     "wtconv_status_string": (ctypes.c_char_p, [_I]),
+    "wtconv_device_status": (_I, [_VP]),
     "wtconv_packed_param_floats": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "wtconv_pack_params": (_I, [_I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _VP, _VP, _VP,
                                 ctypes.POINTER(_VP), ctypes.POINTER(_VP), _VP, _VP]),

@@ -47,21 +47,13 @@ cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, cons
   }
 }
 
-// Planner overrides for tuning sweeps: WTCONV_TUNE="force_tiled,tile_y,tile_x,tile_levels,group,threads,regplane,direct,deep_group"
-// (integers, 0 = automatic).  Read once; absent in normal use.
-const Tuning2d& env_tuning() {
-  static const Tuning2d t = [] {
-    Tuning2d v;
-    if (const char* e = getenv("WTCONV_TUNE")) {
-      int a = 0, b = 0, c = 0, d = 0, g = 0, t = 0, r = 0, ds = 0, dg = 0, cl = 0;
-      sscanf(e, "%d,%d,%d,%d,%d,%d,%d,%d,%d,%d", &a, &b, &c, &d, &g, &t, &r, &ds, &dg, &cl);
-      v.cl = cl;
-      v.force_tiled = a; v.tile_y = b; v.tile_x = c; v.tile_levels = d; v.group = g; v.threads = t; v.regplane = r;
-      v.direct = ds; v.deep_group = dg;
-    }
-    return v;
-  }();
-  return t;
+// Set by the TMA-fed kernels when one of their bounded mbarrier waits gives up (see wt2d_cl.cuh);
+// read and cleared by wtconv_device_status().  One word per device that loads the library.
+__device__ int g_wait_status;
+
+int* wait_status_address() {
+  void* p = nullptr;
+  return cudaGetSymbolAddress(&p, g_wait_status) == cudaSuccess ? static_cast<int*>(p) : nullptr;
 }
 
 int check_common(int C, int K, int L, int dtype) {
@@ -112,7 +104,7 @@ std::shared_ptr<const Chain2d> cached_chain(const Layer2d& ly) {
     for (const Entry& e : entries)
       if (memcmp(&e.key, &key, sizeof(key)) == 0) return e.chain;
   }
-  auto chain = std::make_shared<const Chain2d>(plan_layer(ly, env_tuning()));
+  auto chain = std::make_shared<const Chain2d>(plan_layer(ly));
   std::lock_guard<std::mutex> lock(mu);
   if (entries.size() < kCapacity) entries.push_back({key, chain});
   else { entries[next] = {key, chain}; next = (next + 1) % kCapacity; }
@@ -143,6 +135,7 @@ const char* wtconv_status_string(int status) {
     case WTCONV_ERR_MISALIGNED: return "a tensor pointer is not aligned to its element size";
     case WTCONV_ERR_TOO_LARGE: return "problem too large for the on-chip plan (dimension or shared-memory limit)";
     case WTCONV_ERR_NO_DEVICE: return "no usable sm_100 CUDA device";
+    case WTCONV_ERR_DEVICE_WAIT: return "a kernel gave up waiting for one of its on-chip copies; the outputs of calls since the last status check are invalid";
     case WTCONV_ERR_SCRATCH_LIMIT:
       return "problem needs more scratch than the library's built-in array (WTCONV_STATIC_SCRATCH_BYTES); "
              "use wtconv2d_forward with a caller-provided workspace";
@@ -322,18 +315,36 @@ int wtconv_param_grads(int ndim, int C, int K, int L, int param_dtype, double an
   return (int)launch_param_grads(a, param_dtype, static_cast<cudaStream_t>(stream));
 }
 
+int wtconv_device_status(void* stream) {
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  int word = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(&word, g_wait_status, sizeof(int), 0, cudaMemcpyDeviceToHost, cs);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+  if (e != cudaSuccess) return (int)e;
+  if (word == 0) return WTCONV_OK;
+  const int zero = 0;
+  e = cudaMemcpyToSymbolAsync(g_wait_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, cs);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+  return e == cudaSuccess ? WTCONV_ERR_DEVICE_WAIT : (int)e;
+}
+
 int wtconv2d_workspace_bytes(int B, int C, int H, int W, int K, int L, int dtype, const long long* x_strides,
                              const long long* y_strides, size_t* bytes) {
   if (!bytes) return WTCONV_ERR_BAD_ARG;
   Layer2d ly;
-  // the stage chain depends on the layout (channel-fastest or not) but not on the output
-  // stride or on pointer alignment
+  // The stage chain depends on the strides and on whether the base addresses are 16-byte aligned
+  // (the tensor maps of the channels-last kernels need that).  The size reported is the larger of
+  // both cases, so it holds for any pair of pointers with these strides.
   const int st = make_layer2d(ly, nullptr, nullptr, B, C, H, W, K, L, 1, dtype, x_strides, y_strides);
   if (st) return st;
-  const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
-  const Chain2d& ch = *chp;
-  if (ch.status) return ch.status;
-  *bytes = (size_t)ch.scratch_floats * sizeof(float);
+  long long floats = 0;
+  for (int variant = 0; variant < 2; ++variant) {
+    ly.x_align = ly.y_align = variant ? ly.elem_size : 16;
+    const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
+    if (chp->status) return chp->status;
+    if (chp->scratch_floats > floats) floats = chp->scratch_floats;
+  }
+  *bytes = (size_t)floats * sizeof(float);
   return WTCONV_OK;
 }
 
@@ -366,6 +377,7 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     if (ptr_align(ws) < 16) return WTCONV_ERR_MISALIGNED;
   }
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  int* wait_status = nullptr;
   for (const Reduce2d& rd : ch.reduces) {
     cudaError_t e;
     if (rd.in_off < 0) {
@@ -386,6 +398,7 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
     const float* rin = sg.rin_off < 0 ? nullptr : ws + sg.rin_off;
     float* rout = final_stage ? nullptr : ws + sg.rout_off;
     const int in_dtype = from_x ? dtype : WTCONV_F32;
+    if ((sg.kind == 3 || sg.kind == 4) && !wait_status) wait_status = wait_status_address();
     cudaError_t e;
     switch (sg.kind) {
       case 1:
@@ -395,10 +408,10 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
         e = launch_quad(sg.quad, in_dtype, xin, final_stage ? y : nullptr, rin, rout, packed, (size_t)sg.smem_bytes, cs);
         break;
       case 3:   // input: the layer input or a low-pass plane in the layer's type; output: y or fp32 planes
-        e = launch_cl_level(sg.cl, dtype, xin, rin, final_stage ? y : static_cast<void*>(rout), packed, nullptr, cs);
+        e = launch_cl_level(sg.cl, dtype, xin, rin, final_stage ? y : static_cast<void*>(rout), packed, wait_status, cs);
         break;
       case 4:   // input: the sub-bands of level 2 in the layer's type
-        e = launch_cl_deep(sg.deep, ly.K, dtype, xin, packed, rout, nullptr, cs);
+        e = launch_cl_deep(sg.deep, ly.K, dtype, xin, packed, rout, wait_status, cs);
         break;
       case 5: {
         const int xv = (ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0;
@@ -425,25 +438,15 @@ namespace {
 // their 128-bit accesses are aligned whatever the offsets inside it.
 static __device__ __align__(256) unsigned char g_static_scratch[WTCONV_STATIC_SCRATCH_BYTES];
 
-std::mutex g_scratch_mutex;
-void* g_scratch_addr[kMaxDevices] = {nullptr};   // device address of g_static_scratch, per device
-
 // `g_static_scratch` is only a host-side handle here: kernels need the device address, which
-// differs per device.  Looked up once per device, with that device current.
+// differs per device and does not survive a cudaDeviceReset.  It is therefore asked for on every
+// call (a table lookup in the runtime), with the caller's device current.
 int static_scratch_address(void** out) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
+  void* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDevices) return WTCONV_ERR_NO_DEVICE;
-  std::lock_guard<std::mutex> lock(g_scratch_mutex);
-  if (!g_scratch_addr[dev]) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (e != cudaSuccess) return (int)e;
-    if (!ptr) return WTCONV_ERR_NO_DEVICE;
-    g_scratch_addr[dev] = ptr;
-  }
-  *out = g_scratch_addr[dev];
+  if (!ptr) return WTCONV_ERR_NO_DEVICE;
+  *out = ptr;
   return WTCONV_OK;
 }
 
@@ -454,11 +457,16 @@ extern "C" {
 int wtconv2d_forward_noalloc(const void* x, void* y, const float* packed, int B, int C, int H, int W, int K, int L,
                              int stride, int dtype, const long long* x_strides, const long long* y_strides,
                              void* stream) {
-  // size check first: reject before touching the device
-  size_t need = 0;
-  const int st = wtconv2d_workspace_bytes(B, C, H, W, K, L, dtype, x_strides, y_strides, &need);
+  // size check first, with the chain these very pointers and strides get: reject before touching the device
+  if (!x || !y || !packed) return WTCONV_ERR_BAD_ARG;
+  Layer2d ly;
+  const int st = make_layer2d(ly, x, y, B, C, H, W, K, L, stride, dtype, x_strides, y_strides);
   if (st) return st;
-  if (need > (size_t)WTCONV_STATIC_SCRATCH_BYTES) return WTCONV_ERR_SCRATCH_LIMIT;
+  {
+    const std::shared_ptr<const Chain2d> chp = cached_chain(ly);
+    if (chp->status) return chp->status;
+    if ((size_t)chp->scratch_floats * sizeof(float) > (size_t)WTCONV_STATIC_SCRATCH_BYTES) return WTCONV_ERR_SCRATCH_LIMIT;
+  }
   void* scratch = nullptr;
   const int sa = static_scratch_address(&scratch);
   if (sa) return sa;
@@ -473,6 +481,8 @@ int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, 
   if (st) return st;
   if (B <= 0 || N <= 0 || stride < 1) return WTCONV_ERR_BAD_ARG;
   if (L > kMaxFused) return WTCONV_ERR_BAD_LEVELS;
+  // grid.z carries the sample index, grid.y the channel group; offsets inside a sample are 32-bit
+  if (B > 65535 || (long long)C * N >= (1LL << 31) || (long long)B * C * N >= (1LL << 40)) return WTCONV_ERR_TOO_LARGE;
   if (ptr_align(x) < elem_size(dtype) || ptr_align(y) < elem_size(dtype) || ptr_align(packed) < 16)
     return WTCONV_ERR_MISALIGNED;
   if (N / stride == 0) return WTCONV_OK;   // empty output
@@ -487,11 +497,9 @@ int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, 
   }
   Plan1d p;
   long long smem = 0;
-  // WTCONV_TUNE1D="tile,group": planner overrides for tuning sweeps
-  static const int tune_tx = [] { const char* e = getenv("WTCONV_TUNE1D"); int a = 0, b = 0; if (e) sscanf(e, "%d,%d", &a, &b); return a; }();
-  static const int tune_g = [] { const char* e = getenv("WTCONV_TUNE1D"); int a = 0, b = 0; if (e) sscanf(e, "%d,%d", &a, &b); return b; }();
-  const int ps = plan_1d(p, smem, ly, tune_tx, tune_g);
+  const int ps = plan_1d(p, smem, ly);
   if (ps) return ps;
+  if (p.ngroups > 65535) return WTCONV_ERR_TOO_LARGE;
   return (int)launch_wt1d(p, dtype, x, y, packed, (size_t)smem, static_cast<cudaStream_t>(stream));
 }
 

@@ -72,9 +72,6 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   for (int i = 0; i < 4; ++i) { a.rs[i] = s.rs[i]; a.os[i] = s.os[i]; }
   a.out_vec = s.out_vec; a.rin_vec = s.rin_vec; a.rin_scale = s.rin_scale;
   a.status = status;
-#ifdef WT_CL_TIMING
-  if (const char* e = getenv("WT_CL_DBG")) a.status = reinterpret_cast<int*>(strtoull(e, nullptr, 16));
-#endif
 
   auto kern = wt2d_cl_level_kernel<T, TO, K, NTY, NTX, NS, BASE, MAXREG>;
   constexpr size_t smem = G::smem_bytes;
@@ -91,10 +88,9 @@ template <typename T, typename TO, int K, bool BASE>
 cudaError_t launch_shape(const ClStage& s, const void* x, const float* rin, void* out, const float* packed,
                          int* status, cudaStream_t st) {
   switch (s.config) {
-    case 0: return launch_cfg<T, TO, K, 7, 7, 1, BASE, 152>(s, x, rin, out, packed, status, st);
-    case 1: return launch_cfg<T, TO, K, 4, 7, 1, BASE, 128>(s, x, rin, out, packed, status, st);
-    case 2: return launch_cfg<T, TO, K, 7, 4, 1, BASE, 128>(s, x, rin, out, packed, status, st);
-    case 3: return launch_cfg<T, TO, K, 4, 2, 2, BASE, 168>(s, x, rin, out, packed, status, st);
+    case 0: return launch_cfg<T, TO, K, 4, 7, 1, BASE, 128>(s, x, rin, out, packed, status, st);
+    case 1: return launch_cfg<T, TO, K, 7, 4, 1, BASE, 128>(s, x, rin, out, packed, status, st);
+    case 2: return launch_cfg<T, TO, K, 4, 2, 2, BASE, 168>(s, x, rin, out, packed, status, st);
     default: return launch_cfg<T, TO, K, 2, 1, 4, BASE, 168>(s, x, rin, out, packed, status, st);
   }
 }
@@ -109,9 +105,6 @@ cudaError_t launch_deep_t(const ClDeepArgs& a0, const void* s2, const float* pac
   if (me != cudaSuccess) return me;
   ClDeepArgs a = a0;
   a.packed = packed; a.rout = rout; a.status = status;
-#ifdef WT_CL_TIMING
-  if (const char* e = getenv("WT_CL_DBG2")) a.status = reinterpret_cast<int*>(strtoull(e, nullptr, 16));
-#endif
   auto kern = wt2d_cl_deep_kernel<T, K>;
   static bool done[kMaxDevices] = {false};
   cudaError_t e = allow_full_smem(kern, done);

@@ -14,20 +14,29 @@
 // pixel.
 //
 // Data flow of a CTA:
-//   1. the input frame (band + halo of 2*(K/2) pixels, zero outside the plane: TMA
-//      out-of-bounds fill reproduces both the odd-size padding of wtconv2d.py:49-51
-//      and the 'same' padding of every convolution) arrives through a ring of
-//      cp.async.bulk.tensor chunks of four pixel rows, each completing on an mbarrier;
-//   2. every chunk is turned into one row of the four un-normalised Haar sub-bands
-//      (wavelet.py:62-67 without the tap magnitude, which the packed parameters
-//      carry) and, for the base path, copied pixel by pixel; both arrays are kept in
-//      the tensor's own type (the reference rounds its sub-bands to that type as
-//      well) in a rotated layout that keeps the shared-memory reads of the tiles of
-//      one wavefront in different banks (cl_swizzle);
-//   3. each thread runs the four K x K sub-band convolutions of its tile, adds the
+//   1. one elected thread requests the whole input frame (band + halo of 2*(K/2) pixels)
+//      as four cp.async.bulk.tensor boxes per slot, each completing on its own mbarrier,
+//      and the tap sets of the stage as one cp.async.bulk copy.  Pixels outside the plane
+//      arrive as zeros: TMA out-of-bounds fill reproduces both the odd-size padding of
+//      wtconv2d.py:49-51 and the 'same' padding of every convolution;
+//   2. pass 1 turns pixel rows 2k, 2k+1 into row k of the four Haar sub-bands
+//      (wavelet.py:62-67, at the reference's scale) as fp32 channel pairs.  The sub-bands
+//      overlay the pixel frame in shared memory and are produced last rows first, a batch
+//      at a time (load - barrier - store), so nothing is overwritten before it is read.
+//      Columns are stored rotated by the index of the thread tile they belong to, which
+//      keeps the reads of the tiles served by one 128-byte wavefront in different banks;
+//   3. pass 2: each thread runs the four K x K sub-band convolutions of its tile, adds the
 //      deeper reconstruction to the low-pass result, applies the synthesis butterfly
-//      (wavelet.py:70-75) in registers, accumulates the base convolution and bias
-//      and stores its pixels.  All arithmetic is fp32.
+//      (wavelet.py:70-75) in registers and, for the base path, rebuilds the pixels of its
+//      window from the sub-bands and accumulates the base convolution and bias, then
+//      stores its 4 x 8 pixels.  All arithmetic is fp32.
+//
+// The file also holds the two kernels that feed the top level of a layer with more than one
+// level: wt2d_cl_pyramid_kernel (input -> sub-bands of level 2) and wt2d_cl_deep_kernel
+// (levels 2..L with whole planes on chip -> reconstruction handed to the top level).
+//
+// Every mbarrier wait is bounded (kClWaitSpins); a wait that gives up sets the device status
+// word of ClArgs/ClDeepArgs and the CTA carries on to its end instead of spinning.
 #pragma once
 
 #include <cuda.h>
@@ -227,18 +236,13 @@ struct ClGeo {
   static constexpr size_t smem_bytes = 128 /* alignment slack */ + s_bytes + w_bytes + 64 /* barriers */;
 };
 
-// Rotation swizzle.  A pixel (16 channels) takes 128/SL bytes; the SL thread tiles served by one
-// 128-byte wavefront are consecutive tiles q = ty*NTX + tx of the CTA and all read the same window
-// element.  Storing column f of row r at
-//     (f & ~(SL-1)) + (((f & (SL-1)) + tile_column(f) + NTX * tile_row(r)) & (SL-1))
-// rotates every line by the index of the tile it belongs to, so those SL reads fall into
-// different bank groups; for a reader the rotation is (compile-time part + q) & (SL-1), i.e. one
-// of SL per-thread base pointers plus a compile-time offset.
-template <int SL, int NTX, int TWSH, int TRSH>
-WT_HD int cl_swizzle(int r, int f) {
-  const int rot = ((f >> TWSH) + NTX * (r >> TRSH)) & (SL - 1);
-  return (f & ~(SL - 1)) + (((f & (SL - 1)) + rot) & (SL - 1));
-}
+// Rotation of the sub-band columns.  A position (16 channels, fp32) takes 128/SL bytes; the SL
+// thread tiles served by one 128-byte wavefront are consecutive tiles q = ty*NTX + tx of the CTA
+// and all read the same window element.  Column f of row r is stored at
+//     (f & ~(SL-1)) + ((f + tile_column(f) + NTX * tile_row(r)) & (SL-1)),
+// i.e. every line is rotated by the index of the tile it belongs to, so those SL reads fall into
+// different bank groups; for a reader the rotation is (compile-time part + q) & (SL-1), one of SL
+// per-thread base pointers plus a compile-time offset.
 
 #ifdef __CUDA_ARCH__
 // acc[oy][ox] += sum_{dy,dx} w[dy][dx] * S(oy+dy, ox+dx) for one sub-band of the thread's window.
@@ -336,10 +340,6 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::s_bytes + G::w_bytes);
 
   const int tid = threadIdx.x;
-#ifdef WT_CL_TIMING
-  long long t_start = 0, t_first = 0, t_pass1 = 0;
-  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_start));
-#endif
   // grid: x = band (column band fastest), y = channel group, z = slot group
   const int band = blockIdx.x;
   const int bx = band % a.nbx, by = band / a.nbx;
@@ -400,9 +400,6 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 #pragma unroll 1
   for (int k0 = SR - KU; k0 >= 0; k0 -= KU) {
     for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + KU) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
-#ifdef WT_CL_TIMING
-    if (tid == 0 && k0 == SR - KU) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_first));
-#endif
     raw_t px[KU][NIT][4];
 #pragma unroll
     for (int kk = 0; kk < KU; ++kk)
@@ -438,9 +435,6 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   ok = cl_mbar_wait(&bars[G::NBOX], 0u) && ok;        // tap sets
   if (!ok && a.status) atomicExch(a.status, 1);
   __syncthreads();
-#ifdef WT_CL_TIMING
-  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_pass1));
-#endif
 
   // ---- pass 2: per-thread tile
   const int cp = tid & (kClLanes - 1);
@@ -544,15 +538,6 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       }
     }
   }
-#ifdef WT_CL_TIMING
-  if (tid == 0 && a.status) {
-    long long t_end; unsigned smid;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_end));
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    long long* d = reinterpret_cast<long long*>(a.status) + 8 * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
-    d[0] = t_start; d[1] = t_first; d[2] = t_pass1; d[3] = t_end; d[4] = smid;
-  }
-#endif
 #endif
 }
 
@@ -754,10 +739,6 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const int n0 = blockIdx.y * a.ns;
   const int nset = 1 + 4 * a.nlevels;
   const float* wsrc = a.packed + a.cl_off + (size_t)blockIdx.x * nset * (TAPS * kClGroup);
-#ifdef WT_CL_TIMING
-  long long tt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[0]));
-#endif
 
   if (tid == 0) {
     for (int s = 0; s < 3; ++s) cl_mbar_init(&bars[s], 1);
@@ -777,9 +758,6 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     reinterpret_cast<uint4*>(sm + a.zero_off)[i] = make_uint4(0u, 0u, 0u, 0u);
   __syncthreads();
   bool ok = cl_mbar_wait(&bars[2], 0u);
-#ifdef WT_CL_TIMING
-  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[2]));
-#endif
 
   // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j
   for (int j = 2; j <= a.nlev; ++j) {
@@ -808,9 +786,6 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     __syncthreads();
   }
 
-#ifdef WT_CL_TIMING
-  if (tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[3]));
-#endif
   // ---- pass 3: convolutions + synthesis, deepest level first; the tap sets of the next level are
   // copied while this one is computed
   int cur = 0;
@@ -829,18 +804,8 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     else cl_deep_level<T, K, 1, 2>(a, j, sm, Wsm, c0, n0, tid, nthr);
     __syncthreads();
     cur ^= 1;
-#ifdef WT_CL_TIMING
-    if (tid == 0 && j <= 4) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt[3 + j]));   // tt[4..7]: end of levels 1..4
-#endif
   }
-#ifdef WT_CL_TIMING
-  if (tid == 0 && a.status) {
-    long long* d = reinterpret_cast<long long*>(a.status) + 8 * (blockIdx.y * gridDim.x + blockIdx.x);
-    for (int i = 0; i < 8; ++i) d[i] = tt[i];
-  }
-#else
   if (!ok && a.status) atomicExch(a.status, 1);
-#endif
 #endif
 }
 

@@ -18,11 +18,6 @@ constexpr int kSmemTwoPerSm = 113 * 1024;  // budget that lets two CTAs share on
 constexpr int kThreads2d = 256;
 constexpr int kTiledLevels = 2;            // levels fused per stage when a plane has to be tiled
 
-// Tuning override of the threads per CTA (0 = automatic); process-wide, set by plan_layer.
-inline int& tuning_threads() { static int v = 0; return v; }
-// Direct stores from the top-level items of final stages (see Plan2d::direct_store); process-wide switch
-inline bool& direct_store_enabled() { static bool v = true; return v; }
-
 // thread-tile height for `n` rows out of a menu (largest first): cheapest padded
 // row count, with a small penalty for short tiles (they reuse fewer loaded rows)
 inline int pick_tile(int n, const int* menu, int nmenu, double small_penalty) {
@@ -148,7 +143,6 @@ inline long long layout_stage(Plan2d& p) {
     // 16-bit activations: an eighth warp that takes no item still shortens the staging phases
     // (measured -1 % / -3 % on 56x56 / 28x28 planes; with fp32 activations it costs 4 % at 56x56)
     if (p.elem_size == 2 && p.nthreads > 192) p.nthreads = 256;
-    if (tuning_threads() > 0) p.nthreads = tuning_threads();
   }
   return off * 4;
 }
@@ -309,28 +303,27 @@ inline long long plan_stage(Plan2d& p, const Layer2d& ly, int H, int W, int firs
     // one pixel) writes 16 contiguous bytes, neighbouring channel groups fill the sector in L2
     // (tiles across the whole plane width only: with narrower tiles the scattered stores of a large
     // plane were measured 2.5x slower than the staged, coalesced ones)
-    p.direct_store = (direct_store_enabled() && nlev >= 1 && ly.stride == 1 && p.y_vec == 16 && (ly.C % G) == 0 &&
+    p.direct_store = (nlev >= 1 && ly.stride == 1 && p.y_vec == 16 && (ly.C % G) == 0 &&
                       TX >= W) ? 1 : 0;
   } else {
     // deep stages: the reconstruction block of an item goes straight to the fp32 planes
-    p.direct_store = (direct_store_enabled() && nlev >= 1 && TX >= W) ? 1 : 0;
+    p.direct_store = (nlev >= 1 && TX >= W) ? 1 : 0;
   }
   return layout_stage(p);
 }
 
-// Optional planner overrides (all zero = automatic).  Used by tuning sweeps and by
-// the tests to exercise the tiled multi-stage path on small planes.
+// Optional planner overrides (all zero = automatic).  The shared library always plans with
+// the defaults; the host-emulation test library uses them to exercise the tiled multi-stage
+// path on small planes.
 struct Tuning2d {
   int force_tiled = 0;   // 1: never use the whole-plane mode for the top stage; 2: for no stage
   int tile_y = 0;        // output tile of tiled stages
   int tile_x = 0;
   int tile_levels = 0;   // levels fused per tiled stage
   int group = 0;         // channels per CTA
-  int threads = 0;       // threads per CTA
   int regplane = 0;      // -1: never use the register-level kernels at the bottom; 1: also with other overrides
-  int direct = 0;        // -1: top-level items never store to global memory themselves
   int deep_group = 0;    // channel group of whole-plane stages below the top (0: automatic)
-  int cl = 0;            // -1: never use the channels-last level stage
+  int cl = 0;            // -1: never use the channels-last kernels (they have no host form)
 };
 
 // Whole-plane stage: single tile, all `nlev` levels on chip.  Picks the largest channel
@@ -378,12 +371,11 @@ inline bool cl_stage_supported(const Layer2d& ly) {
 }
 
 // Tile configuration of the channels-last level stage for a W-wide plane (see launch_shape)
-inline int& cl_tall_bands() { static int v = 0; return v; }
 inline int cl_config(int W) {
-  if (W <= 8) return 4;
-  if (W <= 16) return 3;
-  if (W <= 32) return 2;
-  return cl_tall_bands() ? 0 : 1;
+  if (W <= 8) return 3;
+  if (W <= 16) return 2;
+  if (W <= 32) return 1;
+  return 0;
 }
 
 // Description of a channels-last level stage.  level 0 with the base path finishes the layer
@@ -424,8 +416,6 @@ inline void plan_cl_level(ClStage& s, const Layer2d& ly, int level, int H, int W
 // Builds the launch chain of one layer.
 inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) {
   Chain2d ch;
-  tuning_threads() = tune.threads;
-  direct_store_enabled() = tune.direct >= 0;
   // level sizes of the whole pyramid
   std::vector<int> Hl(ly.L + 1), Wl(ly.L + 1);
   Hl[0] = ly.H; Wl[0] = ly.W;
@@ -435,12 +425,11 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // register-resident kernel (channels-last tensors, every remaining level), that kernel
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
   const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly);
-  cl_tall_bands() = (tune.cl == 3 && ly.elem_size == 2) ? 1 : 0;
   // Channels-last tensors larger than 16 x 16 (smaller planes are faster in the register-level
   // kernels below): the sub-band pyramid kernel and a deep stage (whole
   // planes on chip) for the levels below the top one, then the level stage of the top level with
   // the base path.
-  if (use_cl && ly.L >= 1 && (ly.H > 16 || ly.W > 16) && tune.cl != 2) {
+  if (use_cl && ly.L >= 1 && (ly.H > 16 || ly.W > 16)) {
     Stage2d deep;
     bool deep_ok = true;
     if (ly.L >= 2) {

@@ -116,15 +116,36 @@ class _WTConvNd(nn.Module):
             ps += [conv.weight, sc.weight]
         return ps
 
-    def _packed_params(self, device, adjoint=False):
-        """fp32 block of folded parameters (or of the adjoint layer: flipped taps, no bias), rebuilt
-        only when a parameter changed (data pointer, in-place version counter, dtype or device)."""
+    def _param_key(self):
+        """Identity of the parameter values: storage, address, in-place version, dtype."""
         ps = self._kernel_params()
-        key = tuple((p.data_ptr(), p._version) if p is not None else None for p in ps) \
-            + (ps[0].dtype, ps[0].device, self.wt_filter.dtype)
-        cached = self._packed.get(adjoint)
-        if cached is not None and key == self._packed_key.get(adjoint) and cached.device == device:
-            return cached
+        return tuple((p.untyped_storage()._cdata, p.data_ptr(), p._version) if p is not None else None for p in ps) \
+            + (ps[0].dtype, self.wt_filter.dtype)
+
+    def _replicate_for_data_parallel(self):
+        # nn.DataParallel rebuilds its replicas on every forward: their parameters are fresh copies
+        # (new addresses each time) of the master's.  A replica therefore keys its folded block on
+        # the master's parameters; the cache dicts are shared with the master and hold one block
+        # per device, so a device re-packs only after the master's parameters changed.
+        replica = super()._replicate_for_data_parallel()
+        replica._master_key = self._param_key()
+        return replica
+
+    def _packed_params(self, device, adjoint=False):
+        """fp32 block of folded parameters (or of the adjoint layer: flipped taps, no bias), one per
+        device, rebuilt only when a parameter changed (storage, address, in-place version or dtype)."""
+        ps = self._kernel_params()
+        key = getattr(self, "_master_key", None) or self._param_key()
+        slot = (adjoint, device)
+        cached = self._packed.get(slot)
+        if cached is not None and key == self._packed_key.get(slot):
+            packed, event, waited = cached
+            # the block was written on the stream that was current at the time: other streams wait once
+            sid = torch.cuda.current_stream(device).cuda_stream
+            if sid not in waited and not torch.cuda.is_current_stream_capturing():
+                torch.cuda.current_stream(device).wait_event(event)
+                waited.add(sid)
+            return packed
         lib = _lib.load()
         real = [p for p in ps if p is not None]
         pdt = real[0].dtype
@@ -145,13 +166,15 @@ class _WTConvNd(nn.Module):
         ww = arr_t(*[hold[3 + 2 * i].data_ptr() for i in range(L)])
         ws = arr_t(*[hold[4 + 2 * i].data_ptr() for i in range(L)])
         with torch.cuda.device(device):
-            stream = torch.cuda.current_stream(device).cuda_stream
+            cur = torch.cuda.current_stream(device)
             pack = lib.wtconv_pack_params_adjoint if adjoint else lib.wtconv_pack_params
             st = pack(nd, C, K, L, _DTYPE_CODE[pdt], tap, tap,
                       hold[0].data_ptr(), hold[1].data_ptr() if hold[1] is not None else None,
-                      hold[2].data_ptr(), ww, ws, packed.data_ptr(), stream)
-        _lib.check(st, "wtconv_pack_params")
-        self._packed[adjoint], self._packed_key[adjoint] = packed, key
+                      hold[2].data_ptr(), ww, ws, packed.data_ptr(), cur.cuda_stream)
+            _lib.check(st, "wtconv_pack_params")
+            event = torch.cuda.Event()
+            event.record(cur)
+        self._packed[slot], self._packed_key[slot] = (packed, event, {cur.cuda_stream}), key
         return packed
 
     def _check_input(self, x):
