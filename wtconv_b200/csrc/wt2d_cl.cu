@@ -49,6 +49,22 @@ cudaError_t make_map(CUtensorMap& map, const void* x, int B, int C, int H, int W
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Tensor map of the second level's sub-bands, (B, h, w, 4, C): dimensions channel, sub-band, column,
+// row, sample; one box covers the four sub-bands of a whole frame
+template <typename T>
+cudaError_t make_subband_map(CUtensorMap& map, const void* s2, int B, int C, int h, int w, int box_w, int box_h) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cudaErrorNotSupported;
+  const cuuint64_t gdim[5] = {(cuuint64_t)C, 4u, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)B};
+  const cuuint64_t gstr[4] = {(cuuint64_t)C * sizeof(T), (cuuint64_t)4 * C * sizeof(T), (cuuint64_t)w * 4 * C * sizeof(T),
+                              (cuuint64_t)h * w * 4 * C * sizeof(T)};
+  const cuuint32_t box[5] = {(cuuint32_t)kClGroup, 4u, (cuuint32_t)box_w, (cuuint32_t)box_h, 1u};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = enc(&map, TmaType<T>::v, 5, const_cast<void*>(s2), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <typename T, typename TO, int K, int NTY, int NTX, int NS, bool BASE, int MAXREG>
 cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* out, const float* packed, int* status,
                        cudaStream_t stream) {
@@ -98,10 +114,8 @@ cudaError_t launch_shape(const ClStage& s, const void* x, const float* rin, void
 template <typename T, int K>
 cudaError_t launch_deep_t(const ClDeepArgs& a0, const void* s2, const float* packed, float* rout, int* status,
                           cudaStream_t stream) {
-  // tensor map over (channel, column, row, sample * 4 + sub-band) of the dense sub-band planes
-  const long long xs[4] = {(long long)a0.h[1] * a0.w[1] * a0.C, 1, (long long)a0.w[1] * a0.C, a0.C};
   CUtensorMap map;
-  cudaError_t me = make_map<T>(map, s2, a0.B * 4, a0.C, a0.h[1], a0.w[1], xs, a0.spitch[1], a0.srows[1]);
+  cudaError_t me = make_subband_map<T>(map, s2, a0.B, a0.C, a0.h[1], a0.w[1], a0.spitch[1], a0.srows[1]);
   if (me != cudaSuccess) return me;
   ClDeepArgs a = a0;
   a.packed = packed; a.rout = rout; a.status = status;

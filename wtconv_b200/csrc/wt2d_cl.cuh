@@ -109,6 +109,14 @@ __device__ __forceinline__ void cl_tma_load4(void* dst, const CUtensorMap* map, 
       : "memory");
 }
 
+// 5-D tiled TMA load (channel, sub-band, column, row, sample) -> shared memory, completing on `bar`
+__device__ __forceinline__ void cl_tma_load5(void* dst, const CUtensorMap* map, void* bar, int c, int sb, int x, int y, int n) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(cl_smem_addr(dst)), "l"(map), "r"(cl_smem_addr(bar)), "r"(c), "r"(sb), "r"(x), "r"(y), "r"(n)
+      : "memory");
+}
+
 // One 2 x 2 Haar analysis step at the reference's scale (wavelet.py:27-30 with tap 1/2):
 // sb = {LL, LH, HL, HH} = 1/2 {a+b+c+d, a+b-c-d, a-b+c-d, a-b-c+d}
 __device__ __forceinline__ void cl_haar(float2 a, float2 b, float2 c, float2 d, float2 (&sb)[4]) {
@@ -219,9 +227,19 @@ struct ClGeo {
   static constexpr int NBOX = 4;                            // TMA boxes per slot, stacked along the rows
   static constexpr int BOXR = XR / NBOX;                    // pixel rows per box
   static_assert(XR % NBOX == 0, "the pixel frame is a whole number of boxes");
-  static constexpr int NIT1 = (NS * SC * kClLanes + (NTY * NTX * NS * kClLanes + 31) / 32 * 32 - 1) / ((NTY * NTX * NS * kClLanes + 31) / 32 * 32);   // blocks per thread and row
-  static constexpr int KU = (SR % 4 == 0 && NIT1 <= 2) ? 4 : 2;   // sub-band rows per batch of pass 1
-  static_assert(SR % KU == 0, "pass 1 works in whole batches");
+  // batches of pass 1: the fewest (a divisor of SR) that keep a thread's share of a batch within
+  // 64 registers of raw pixels (four pixels per block; one register per 16-bit pair, two per fp32 pair)
+  static constexpr int pick_batches() {
+    const int nt = (NTY * NTX * NS * kClLanes + 31) / 32 * 32;
+    const int most = sizeof(T) == 2 ? 16 : 8;   // blocks per thread and batch
+    for (int nb = 1; nb <= SR; ++nb) {
+      if (SR % nb) continue;
+      const int items = NS * (SR / nb) * SC * kClLanes;
+      if ((items + nt - 1) / nt <= most) return nb;
+    }
+    return SR;
+  }
+  static constexpr int NB = pick_batches();
   static constexpr int NT = (NTY * NTX * NS * kClLanes + 31) / 32 * 32;   // threads per CTA (whole warps)
   static constexpr int TAPS = K * K + 1;                    // staged floats per tap set and channel (last: bias slot)
   static constexpr int SL = 128 / (kClGroup * (int)sizeof(float));   // sub-band positions per 128-byte line
@@ -331,7 +349,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 #ifdef __CUDA_ARCH__
   typedef ClGeo<T, K, NTY, NTX, NS> G;
   typedef typename ClPair<T>::raw_t raw_t;
-  constexpr int SC = G::SC, SR = G::SR, HS = G::HS, SL = G::SL, XC = G::XC, KU = G::KU;
+  constexpr int SC = G::SC, SR = G::SR, HS = G::HS, SL = G::SL, XC = G::XC;
   static_assert(kClRH == 2 && kClCW == 4, "the swizzle assumes 2 x 4 thread tiles");
   extern __shared__ unsigned char cl_smem_raw[];
   unsigned char* sm = cl_smem_raw + ((128u - (cl_smem_addr(cl_smem_raw) & 127u)) & 127u);
@@ -375,61 +393,54 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   __syncthreads();     // barrier words initialised before anyone waits on them
 
   // ---- pass 1: pixel rows 2k, 2k+1 of the frame -> row k of the four sub-bands (one Haar step at
-  // the reference's scale).  Batches of KU rows, last rows first: a batch is read into registers,
-  // the CTA meets, and only then are its sub-band rows written -- they cover frame rows of this
-  // and of earlier batches only (a sub-band row takes at least the bytes of its two pixel rows and
-  // both arrays start at the same address).  A thread keeps the same blocks (slot, column,
-  // channel pair) in every batch.
-  constexpr int ITEMS = NS * SC * kClLanes;
-  constexpr int NIT = (ITEMS + G::NT - 1) / G::NT;
-  int fcol[NIT];
-  float* sdst[NIT];
-  const T* fsrc[NIT];
-#pragma unroll
-  for (int j = 0; j < NIT; ++j) {
-    const int it = tid + j * G::NT;
-    const int cpj = it & (kClLanes - 1);
-    const int blk = it >> 3;
-    const int f = blk % SC;
-    const int slot = blk / SC;
-    fcol[j] = (it < ITEMS) ? f : -1;
-    sdst[j] = S + (size_t)slot * G::SLOT_S + 2 * cpj;
-    fsrc[j] = reinterpret_cast<const T*>(S + (size_t)slot * G::SLOT_S) + (size_t)(2 * f) * kClGroup + 2 * cpj;
-  }
+  // the reference's scale).  The blocks (slot, row, column, channel pair) of a batch of rows are
+  // dealt round-robin to the threads; a batch is read into registers, the CTA meets, and only then
+  // are its sub-band rows written -- they cover frame rows of this and of later batches only (a
+  // sub-band row takes at least the bytes of its two pixel rows and both arrays start at the same
+  // address), and batches run last rows first.  16-bit frames fit the registers in one batch.
+  constexpr int NB = G::NB, RB = SR / NB;
+  constexpr int BITEMS = NS * RB * SC * kClLanes;
+  constexpr int NIT = (BITEMS + G::NT - 1) / G::NT;
   bool ok = true;
 #pragma unroll 1
-  for (int k0 = SR - KU; k0 >= 0; k0 -= KU) {
-    for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + KU) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
-    raw_t px[KU][NIT][4];
+  for (int bt = NB - 1; bt >= 0; --bt) {
+    const int k0 = bt * RB;
+    for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + RB) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
+    raw_t px[NIT][4];
 #pragma unroll
-    for (int kk = 0; kk < KU; ++kk)
-#pragma unroll
-      for (int j = 0; j < NIT; ++j) {
-        if (fcol[j] < 0) continue;
-        const T* p = fsrc[j] + (size_t)(2 * (k0 + kk)) * XC * kClGroup;
-        px[kk][j][0] = ClPair<T>::load_raw(p);
-        px[kk][j][1] = ClPair<T>::load_raw(p + kClGroup);
-        px[kk][j][2] = ClPair<T>::load_raw(p + XC * kClGroup);
-        px[kk][j][3] = ClPair<T>::load_raw(p + XC * kClGroup + kClGroup);
-      }
+    for (int j = 0; j < NIT; ++j) {
+      const int it = tid + j * G::NT;
+      if (it >= BITEMS) continue;
+      const int cpj = it & (kClLanes - 1);
+      const int blk = it >> 3;
+      const int f = blk % SC;
+      const int t = blk / SC;
+      const int k = k0 + t % RB;
+      const int slot = t / RB;
+      const T* p = reinterpret_cast<const T*>(S + (size_t)slot * G::SLOT_S) + ((size_t)(2 * k) * XC + 2 * f) * kClGroup + 2 * cpj;
+      px[j][0] = ClPair<T>::load_raw(p);
+      px[j][1] = ClPair<T>::load_raw(p + kClGroup);
+      px[j][2] = ClPair<T>::load_raw(p + XC * kClGroup);
+      px[j][3] = ClPair<T>::load_raw(p + XC * kClGroup + kClGroup);
+    }
     __syncthreads();
 #pragma unroll
-    for (int kk = 0; kk < KU; ++kk) {
-      const int k = k0 + kk;
-      const int rrot = NTX * (k >> 1);
+    for (int j = 0; j < NIT; ++j) {
+      const int it = tid + j * G::NT;
+      if (it >= BITEMS) continue;
+      const int cpj = it & (kClLanes - 1);
+      const int blk = it >> 3;
+      const int f = blk % SC;
+      const int t = blk / SC;
+      const int k = k0 + t % RB;
+      const int slot = t / RB;
+      float2 sb[4];
+      cl_haar(ClPair<T>::widen(px[j][0]), ClPair<T>::widen(px[j][1]), ClPair<T>::widen(px[j][2]), ClPair<T>::widen(px[j][3]), sb);
+      const int rot = ((f >> 2) + NTX * (k >> 1)) & (SL - 1);
+      const int fs = (f & ~(SL - 1)) + ((f + rot) & (SL - 1));
+      float* d = S + (size_t)slot * G::SLOT_S + (size_t)k * G::ROWS + fs * kClGroup + 2 * cpj;
 #pragma unroll
-      for (int j = 0; j < NIT; ++j) {
-        const int f = fcol[j];
-        if (f < 0) continue;
-        float2 sb[4];
-        cl_haar(ClPair<T>::widen(px[kk][j][0]), ClPair<T>::widen(px[kk][j][1]), ClPair<T>::widen(px[kk][j][2]),
-                ClPair<T>::widen(px[kk][j][3]), sb);
-        const int rot = ((f >> 2) + rrot) & (SL - 1);
-        const int fs = (f & ~(SL - 1)) + ((f + rot) & (SL - 1));
-        float* d = sdst[j] + (size_t)k * G::ROWS + fs * kClGroup;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) *reinterpret_cast<float2*>(d + s * G::SUBS) = sb[s];
-      }
+      for (int sbi = 0; sbi < 4; ++sbi) *reinterpret_cast<float2*>(d + sbi * G::SUBS) = sb[sbi];
     }
   }
   ok = cl_mbar_wait(&bars[G::NBOX], 0u) && ok;        // tap sets
@@ -546,8 +557,8 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 //
 // One thread owns one channel pair of one 4 x 4 pixel block: the four 2 x 2 blocks give four
 // values of the first level's low-pass plane LL_1 (never stored) and their Haar step gives one
-// position of S_2 = {LL_2, LH_2, HL_2, HH_2}, written as (B, 4, h, w, C) planes in the input's
-// type at the reference's scale.  Channel pairs are the fastest thread index, so a warp reads
+// position of S_2 = {LL_2, LH_2, HL_2, HH_2}, written as (B, h, w, 4, C) in the input's type at
+// the reference's scale (the four sub-bands of a position are neighbours in memory).  Channel pairs are the fastest thread index, so a warp reads
 // and writes 128 contiguous bytes per pixel.  Pixels outside the plane count as zeros
 // (wtconv2d.py:49-51).
 // ---------------------------------------------------------------------------
@@ -557,7 +568,7 @@ struct ClPyramidArgs {
   int x_vec;            // 1: channel pairs may be loaded as one word
   int B, C, H, W;
   int h2, w2;           // size of the second level's sub-bands: ceil(ceil(H/2)/2), ...
-  void* s2;             // (B, 4, h2, w2, C)
+  void* s2;             // (B, h2, w2, 4, C)
   long long total;      // B * h2 * w2 * ceil(C/2)
 };
 
@@ -593,12 +604,11 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
       }
     float2 sb[4];
     cl_haar(l[0][0], l[0][1], l[1][0], l[1][1], sb);
-    const size_t plane = (size_t)a.h2 * a.w2 * a.C;
-    T* d = static_cast<T*>(a.s2) + (size_t)n * 4 * plane + ((size_t)k * a.w2 + f) * a.C + c;
+    T* d = static_cast<T*>(a.s2) + (((size_t)n * a.h2 + k) * a.w2 + f) * 4 * a.C + c;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      if (both && (a.C & 1) == 0) ClPair<T>::store(d + s * plane, sb[s]);
-      else { d[s * plane] = Elem<T>::from_f(sb[s].x); if (both) d[s * plane + 1] = Elem<T>::from_f(sb[s].y); }
+      if (both && (a.C & 1) == 0) ClPair<T>::store(d + (size_t)s * a.C, sb[s]);
+      else { d[(size_t)s * a.C] = Elem<T>::from_f(sb[s].x); if (both) d[(size_t)s * a.C + 1] = Elem<T>::from_f(sb[s].y); }
     }
   }
 #endif
@@ -608,128 +618,127 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 // Deep stage: every level from the second one down, whole planes on chip.
 //
 // A CTA owns NS plane slots (sample, 16-channel group).  The sub-bands of the second level
-// (from the pyramid kernel) arrive as one TMA box per sub-band, with the zero border the
+// (from the pyramid kernel) arrive as one 5-D TMA box per slot, with the zero border the
 // convolutions need supplied by the out-of-bounds fill.  The analyses of the deeper levels,
 // the sub-band convolutions and the synthesis of every level then run out of shared memory,
 // deepest level first, and the reconstruction that the top level adds to its low-pass result
 // (wtconv2d.py:64-76) leaves as fp32 channels-last planes.
 //
 // On-chip level j = 1..nlev is layer level j+1.  S_j: frame of (h_j + 2*HS) x (w_j + 2*HS)
-// positions (rounded up to whole thread tiles) with a zero border, four sub-bands, kept in
-// the input's type at the reference's scale; R_j: fp32 reconstruction of level j,
-// h_{j-1} x w_{j-1}.
+// positions (rounded up to whole thread tiles) with a zero border, stored
+// [row][column][sub-band][16 channels] in the input's type at the reference's scale;
+// R_j: fp32 reconstruction of level j, h_{j-1} x w_{j-1} positions of 16 channels.
+//
+// A warp owns one tile of RT x CT positions: lane = (sub-band, channel pair), so the four
+// sub-band convolutions of a tile run side by side, a warp reads one contiguous 128-byte
+// (16-bit) or 256-byte (fp32) line per position, and the synthesis butterfly
+// (wavelet.py:70-75) is two xor-shuffles across the sub-band bits of the lane index.
 // ---------------------------------------------------------------------------
+constexpr int kClDeepSetPitch = (5 * 5 + 1) * kClGroup * 4 + 32;   // bytes between the staged tap sets of a level (K = 5):
+                                                                  // 32 past a multiple of 128, so the four sets read by a warp fall into different banks
+constexpr int kClDeepLevelBytes = (4 * kClDeepSetPitch + 127) / 128 * 128;
+
 #ifdef __CUDA_ARCH__
-// Sub-band convolutions + synthesis of level j for every thread tile of the CTA's slots.
+// Sub-band convolutions + synthesis of level j for every tile of the CTA's slots.
 template <typename T, int K, int RT, int CT>
-__device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsigned char* sm, const float2* Wsm,
+__device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsigned char* sm, const unsigned char* wlev,
                                               int c0, int n0, int tid, int nthr) {
-  constexpr int TAPS = K * K + 1;
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int POS = 4 * kClGroup;                 // elements per frame position
+  const int lane = tid & 31, sbi = lane >> 3, cp = lane & (kClLanes - 1);
+  const int warp = tid >> 5, nwarp = nthr >> 5;
   const int hj = a.h[j], wj = a.w[j], hp = a.h[j - 1], wp = a.w[j - 1];
   const int tyn = cdiv(hj, RT), txn = cdiv(wj, CT);
   const int ntile = a.ns * tyn * txn;
-  const int pitch = a.spitch[j], sub = a.ssub[j];
+  const int pitch = a.spitch[j];
   const T* Sj = reinterpret_cast<const T*>(sm + a.soff[j]);
   const float* Rin = (j < a.nlev) ? reinterpret_cast<const float*>(sm + a.roff[j + 1]) : nullptr;
   float* Rout = (j > 1) ? reinterpret_cast<float*>(sm + a.roff[j]) : nullptr;
-  const int cp = tid & (kClLanes - 1);
-  for (int q = tid >> 3; q < ntile; q += nthr >> 3) {
+  // taps of this lane's sub-band and channel pair: once per level
+  float2 wr[K * K];
+  {
+    const float2* w = reinterpret_cast<const float2*>(wlev + sbi * kClDeepSetPitch) + cp;
+#pragma unroll
+    for (int t = 0; t < K * K; ++t) wr[t] = w[t * kClLanes];
+  }
+  const bool neg0 = (sbi & 1) != 0, neg1 = (sbi & 2) != 0;
+  for (int q = warp; q < ntile; q += nwarp) {      // warp-uniform bound: every lane takes part in the shuffles
     const int slot = q / (tyn * txn);
     const int rem = q - slot * (tyn * txn);
     const int ty = rem / txn, tx = rem - ty * txn;
     const int gi = ty * RT, gj = tx * CT;
-    float2 acc[4][RT][CT];
+    float2 y[RT][CT];
 #pragma unroll
-    for (int s = 0; s < 4; ++s)
+    for (int i = 0; i < RT; ++i)
 #pragma unroll
-      for (int i = 0; i < RT; ++i)
-#pragma unroll
-        for (int jj = 0; jj < CT; ++jj) acc[s][i][jj] = make_float2(0.f, 0.f);
-    if (Rin) {
+      for (int jj = 0; jj < CT; ++jj) y[i][jj] = make_float2(0.f, 0.f);
+    if (Rin && sbi == 0) {                         // the deeper reconstruction joins the low-pass result
       const float* rb = Rin + (size_t)slot * a.rslot[j + 1] + 2 * cp;
 #pragma unroll
       for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int jj = 0; jj < CT; ++jj)
           if (gi + i < hj && gj + jj < wj)
-            acc[0][i][jj] = __fmul2_rn(*reinterpret_cast<const float2*>(rb + ((gi + i) * wj + gj + jj) * kClGroup),
-                                       make_float2(0.5f, 0.5f));
+            y[i][jj] = __fmul2_rn(*reinterpret_cast<const float2*>(rb + ((gi + i) * wj + gj + jj) * kClGroup),
+                                  make_float2(0.5f, 0.5f));
     }
-    const T* win = Sj + (size_t)slot * a.sslot[j] + ((size_t)gi * pitch + gj) * kClGroup + 2 * cp;
-#pragma unroll 1
-    for (int s = 0; s < 4; ++s) {
-      const float2* w = Wsm + s * TAPS * kClLanes + cp;
-      const T* ws = win + (size_t)s * sub;
-      float2 wr[K * K];
+    const T* win = Sj + (size_t)slot * a.sslot[j] + ((size_t)gi * pitch + gj) * POS + sbi * kClGroup + 2 * cp;
 #pragma unroll
-      for (int t = 0; t < K * K; ++t) wr[t] = w[t * kClLanes];
-      float2 y[RT][CT];
+    for (int iy = 0; iy < RT + K - 1; ++iy) {
+      float2 in[CT + K - 1];
 #pragma unroll
-      for (int i = 0; i < RT; ++i)
+      for (int c = 0; c < CT + K - 1; ++c) in[c] = ClPair<T>::load(win + (iy * pitch + c) * POS);
 #pragma unroll
-        for (int jj = 0; jj < CT; ++jj) y[i][jj] = make_float2(0.f, 0.f);
+      for (int dy = 0; dy < K; ++dy) {
+        const int oy = iy - dy;
+        if (oy >= 0 && oy < RT) {
 #pragma unroll
-      for (int iy = 0; iy < RT + K - 1; ++iy) {
-        float2 in[CT + K - 1];
+          for (int dx = 0; dx < K; ++dx)
 #pragma unroll
-        for (int c = 0; c < CT + K - 1; ++c) in[c] = ClPair<T>::load(ws + (iy * pitch + c) * kClGroup);
-#pragma unroll
-        for (int dy = 0; dy < K; ++dy) {
-          const int oy = iy - dy;
-          if (oy >= 0 && oy < RT) {
-#pragma unroll
-            for (int dx = 0; dx < K; ++dx)
-#pragma unroll
-              for (int ox = 0; ox < CT; ++ox) y[oy][ox] = cl_fma2(in[ox + dx], wr[dy * K + dx], y[oy][ox]);
-          }
+            for (int ox = 0; ox < CT; ++ox) y[oy][ox] = cl_fma2(in[ox + dx], wr[dy * K + dx], y[oy][ox]);
         }
       }
-#pragma unroll
-      for (int i = 0; i < RT; ++i)
-#pragma unroll
-        for (int jj = 0; jj < CT; ++jj) {
-          // the loop over s is kept rolled (four times less code); select the accumulator set by s
-          if (s == 0) acc[0][i][jj] = cl_add2(acc[0][i][jj], y[i][jj]);
-          else if (s == 1) acc[1][i][jj] = y[i][jj];
-          else if (s == 2) acc[2][i][jj] = y[i][jj];
-          else acc[3][i][jj] = y[i][jj];
-        }
     }
+    // synthesis: out(2i+dy, 2j+dx) = LL + (-1)^dy LH + (-1)^dx HL + (-1)^(dy+dx) HH.  Two butterfly
+    // stages over the sub-band bits of the lane; afterwards the lane of "sub-band" k holds the
+    // pixel with dy = k & 1, dx = k >> 1.
     const int n = n0 + slot;
+    const int dy = sbi & 1, dx = sbi >> 1;
 #pragma unroll
     for (int i = 0; i < RT; ++i)
 #pragma unroll
       for (int jj = 0; jj < CT; ++jj) {
-        const float2 ll = acc[0][i][jj], lh = acc[1][i][jj], hl = acc[2][i][jj], hh = acc[3][i][jj];
-        const float2 pp = cl_add2(ll, lh), qq = cl_sub2(ll, lh), uu = cl_add2(hl, hh), vv = cl_sub2(hl, hh);
-        const float2 o[2][2] = {{cl_add2(pp, uu), cl_sub2(pp, uu)}, {cl_add2(qq, vv), cl_sub2(qq, vv)}};
-#pragma unroll
-        for (int dy = 0; dy < 2; ++dy)
-#pragma unroll
-          for (int dx = 0; dx < 2; ++dx) {
-            const int yy = 2 * (gi + i) + dy, xx = 2 * (gj + jj) + dx;
-            if (yy < hp && xx < wp) {
-              if (Rout) {
-                *reinterpret_cast<float2*>(Rout + (size_t)slot * a.rslot[j] + (yy * wp + xx) * kClGroup + 2 * cp) = o[dy][dx];
-              } else if (n < a.B && c0 + 2 * cp < a.C) {
-                float* g = a.rout + (((size_t)n * hp + yy) * wp + xx) * a.C + c0 + 2 * cp;
-                if (c0 + 2 * cp + 1 < a.C && (a.C & 1) == 0) *reinterpret_cast<float2*>(g) = o[dy][dx];
-                else { g[0] = o[dy][dx].x; if (c0 + 2 * cp + 1 < a.C) g[1] = o[dy][dx].y; }
-              }
-            }
+        float2 v = y[i][jj], o;
+        o.x = __shfl_xor_sync(kFull, v.x, 8);
+        o.y = __shfl_xor_sync(kFull, v.y, 8);
+        v = neg0 ? cl_sub2(o, v) : cl_add2(v, o);
+        o.x = __shfl_xor_sync(kFull, v.x, 16);
+        o.y = __shfl_xor_sync(kFull, v.y, 16);
+        v = neg1 ? cl_sub2(o, v) : cl_add2(v, o);
+        const int yy = 2 * (gi + i) + dy, xx = 2 * (gj + jj) + dx;
+        if (yy < hp && xx < wp) {
+          if (Rout) {
+            *reinterpret_cast<float2*>(Rout + (size_t)slot * a.rslot[j] + (yy * wp + xx) * kClGroup + 2 * cp) = v;
+          } else if (n < a.B && c0 + 2 * cp < a.C) {
+            float* g = a.rout + (((size_t)n * hp + yy) * wp + xx) * a.C + c0 + 2 * cp;
+            if (c0 + 2 * cp + 1 < a.C && (a.C & 1) == 0) *reinterpret_cast<float2*>(g) = v;
+            else { g[0] = v.x; if (c0 + 2 * cp + 1 < a.C) g[1] = v.y; }
           }
+        }
       }
   }
 }
 #endif
 
 template <typename T, int K>
-__global__ void __launch_bounds__(kClDeepThreads, 1)
+__global__ void __launch_bounds__(kClDeepThreads, 2)
 wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ ClDeepArgs a) {
 #ifdef __CUDA_ARCH__
+  static_assert(K == 5, "the staged tap sets are laid out for K = 5");
   constexpr int HS = K / 2;
   constexpr int TAPS = K * K + 1;
-  constexpr unsigned kLevelBytes = 4u * TAPS * kClGroup * sizeof(float);
+  constexpr int POS = 4 * kClGroup;
+  constexpr unsigned kSetBytes = (unsigned)(TAPS * kClGroup * sizeof(float));
   extern __shared__ unsigned char cl_smem_raw[];
   unsigned char* sm = cl_smem_raw + ((128u - (cl_smem_addr(cl_smem_raw) & 127u)) & 127u);
   unsigned char* wbuf = sm + a.woff;                 // two buffers of the four tap sets of a level
@@ -740,18 +749,22 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const int nset = 1 + 4 * a.nlevels;
   const float* wsrc = a.packed + a.cl_off + (size_t)blockIdx.x * nset * (TAPS * kClGroup);
 
+  // the four tap sets of on-chip level j (layer level index j, 0-based) -> buffer `buf`
+  auto load_taps = [&](int j, int buf) {
+    cl_mbar_expect_tx(&bars[buf], 4u * kSetBytes);
+    for (int sb = 0; sb < 4; ++sb)
+      cl_bulk_load(wbuf + (size_t)buf * kClDeepLevelBytes + (size_t)sb * kClDeepSetPitch,
+                   wsrc + (size_t)(1 + 4 * j + sb) * (TAPS * kClGroup), kSetBytes, &bars[buf]);
+  };
+
   if (tid == 0) {
     for (int s = 0; s < 3; ++s) cl_mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // S_1 of every slot: one box per sub-band, starting HS positions outside the plane
-    cl_mbar_expect_tx(&bars[2], (unsigned)(a.ns * 4 * a.ssub[1] * (int)sizeof(T)));
+    // S_1 of every slot: one box over the four sub-bands, starting HS positions outside the plane
+    cl_mbar_expect_tx(&bars[2], (unsigned)(a.ns * a.sslot[1] * (int)sizeof(T)));
     for (int sl = 0; sl < a.ns; ++sl)
-      for (int sb = 0; sb < 4; ++sb)
-        cl_tma_load4(sm + a.soff[1] + ((size_t)sl * a.sslot[1] + (size_t)sb * a.ssub[1]) * sizeof(T), &xmap, &bars[2], c0,
-                     -HS, -HS, (n0 + sl) * 4 + sb);
-    // tap sets of the deepest level (layer level 1 + nlev, 0-based index nlev)
-    cl_mbar_expect_tx(&bars[0], kLevelBytes);
-    cl_bulk_load(wbuf, wsrc + (size_t)(1 + 4 * a.nlev) * (TAPS * kClGroup), kLevelBytes, &bars[0]);
+      cl_tma_load5(sm + a.soff[1] + (size_t)sl * a.sslot[1] * sizeof(T), &xmap, &bars[2], c0, 0, -HS, -HS, n0 + sl);
+    load_taps(a.nlev, 0);                            // deepest level first
   }
   // zero borders (and overhang) of the deeper frames (S_1 is filled whole by the TMA boxes)
   for (int i = tid; i < a.zero_bytes / 16; i += nthr)
@@ -759,31 +772,33 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   bool ok = cl_mbar_wait(&bars[2], 0u);
 
-  // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j
-  for (int j = 2; j <= a.nlev; ++j) {
-    const T* Sp = reinterpret_cast<const T*>(sm + a.soff[j - 1]);
-    T* Sj = reinterpret_cast<T*>(sm + a.soff[j]);
-    const int hj = a.h[j], wj = a.w[j], pp_ = a.spitch[j - 1], pj = a.spitch[j], sub = a.ssub[j];
-    const int items = a.ns * hj * wj * kClLanes;
-    for (int it = tid; it < items; it += nthr) {
-      const int cp = it & (kClLanes - 1);
-      const int blk = it >> 3;
-      const int f = blk % wj;
-      const int r = (blk / wj) % hj;
-      const int slot = blk / (wj * hj);
-      // positions (2r, 2f) .. (2r+1, 2f+1) of the low-pass band; beyond the plane the frame holds zeros
-      const T* p = Sp + (size_t)slot * a.sslot[j - 1] + ((size_t)(2 * r + HS) * pp_ + 2 * f + HS) * kClGroup + 2 * cp;
-      const float2 va = ClPair<T>::load(p), vb = ClPair<T>::load(p + kClGroup);
-      const float2 vc = ClPair<T>::load(p + (size_t)pp_ * kClGroup), vd = ClPair<T>::load(p + (size_t)pp_ * kClGroup + kClGroup);
-      float2 sb[4];
-      cl_haar(va, vb, vc, vd, sb);
-      T* d = Sj + (size_t)slot * a.sslot[j] + ((size_t)(r + HS) * pj + f + HS) * kClGroup + 2 * cp;
-      ClPair<T>::store(d, sb[0]);
-      ClPair<T>::store(d + sub, sb[1]);
-      ClPair<T>::store(d + 2 * (size_t)sub, sb[2]);
-      ClPair<T>::store(d + 3 * (size_t)sub, sb[3]);
+  // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j.  A warp owns a
+  // position; its lane (sub-band, channel pair) forms one sub-band of one channel pair.
+  {
+    const int lane = tid & 31, sbi = lane >> 3, cp = lane & (kClLanes - 1);
+    const float2 h = make_float2(0.5f, 0.5f);
+    const float2 s1 = (sbi & 2) ? make_float2(-1.f, -1.f) : make_float2(1.f, 1.f);      // a -+ b, c -+ d
+    const float2 s2 = (sbi & 1) ? make_float2(-0.5f, -0.5f) : make_float2(0.5f, 0.5f);   // +- the lower row
+    for (int j = 2; j <= a.nlev; ++j) {
+      const T* Sp = reinterpret_cast<const T*>(sm + a.soff[j - 1]);
+      T* Sj = reinterpret_cast<T*>(sm + a.soff[j]);
+      const int hj = a.h[j], wj = a.w[j], pp_ = a.spitch[j - 1], pj = a.spitch[j];
+      const int items = a.ns * hj * wj;
+      for (int it = tid >> 5; it < items; it += nthr >> 5) {
+        const int f = it % wj;
+        const int r = (it / wj) % hj;
+        const int slot = it / (wj * hj);
+        // positions (2r, 2f) .. (2r+1, 2f+1) of the low-pass band; beyond the plane the frame holds zeros
+        const T* p = Sp + (size_t)slot * a.sslot[j - 1] + ((size_t)(2 * r + HS) * pp_ + 2 * f + HS) * POS + 2 * cp;
+        const float2 va = ClPair<T>::load(p), vb = ClPair<T>::load(p + POS);
+        const float2 vc = ClPair<T>::load(p + (size_t)pp_ * POS), vd = ClPair<T>::load(p + (size_t)pp_ * POS + POS);
+        // the same arithmetic as cl_haar, for this lane's sub-band only
+        const float2 top = cl_fma2(vb, s1, va), bot = cl_fma2(vd, s1, vc);
+        const float2 v = cl_fma2(top, h, __fmul2_rn(bot, s2));
+        ClPair<T>::store(Sj + (size_t)slot * a.sslot[j] + ((size_t)(r + HS) * pj + f + HS) * POS + sbi * kClGroup + 2 * cp, v);
+      }
+      __syncthreads();
     }
-    __syncthreads();
   }
 
   // ---- pass 3: convolutions + synthesis, deepest level first; the tap sets of the next level are
@@ -793,15 +808,13 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   for (int j = a.nlev; j >= 1; --j) {
     if (tid == 0 && j > 1) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the other buffer was read two levels ago
-      cl_mbar_expect_tx(&bars[1 - cur], kLevelBytes);
-      cl_bulk_load(wbuf + (size_t)(1 - cur) * kLevelBytes, wsrc + (size_t)(1 + 4 * (j - 1)) * (TAPS * kClGroup),
-                   kLevelBytes, &bars[1 - cur]);
+      load_taps(j - 1, 1 - cur);
     }
     ok = cl_mbar_wait(&bars[cur], wphase[cur]) && ok;
     wphase[cur] ^= 1u;
-    const float2* Wsm = reinterpret_cast<const float2*>(wbuf + (size_t)cur * kLevelBytes);
-    if (a.h[j] * a.w[j] >= 32) cl_deep_level<T, K, kClRH, kClCW>(a, j, sm, Wsm, c0, n0, tid, nthr);
-    else cl_deep_level<T, K, 1, 2>(a, j, sm, Wsm, c0, n0, tid, nthr);
+    const unsigned char* wlev = wbuf + (size_t)cur * kClDeepLevelBytes;
+    if (a.h[j] * a.w[j] >= 32) cl_deep_level<T, K, kClRH, kClCW>(a, j, sm, wlev, c0, n0, tid, nthr);
+    else cl_deep_level<T, K, 1, 2>(a, j, sm, wlev, c0, n0, tid, nthr);
     __syncthreads();
     cur ^= 1;
   }

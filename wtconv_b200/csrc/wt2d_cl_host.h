@@ -10,7 +10,7 @@ constexpr int kClGroup = 16;          // channels per plane slot
 constexpr int kClLanes = 8;           // lanes (channel pairs) per thread tile
 constexpr int kClRH = 2, kClCW = 4;   // sub-band positions per thread tile
 constexpr int kClDeepMaxLev = 8;      // levels the deep stage can hold on chip
-constexpr int kClDeepThreads = 512;
+constexpr int kClDeepThreads = 256;    // eight warps; two CTAs share an SM when their frames fit
 
 struct ClStage {
   int B, C, H, W;        // input plane set of the level (channels-last)
@@ -42,8 +42,8 @@ struct ClDeepArgs {
   int w[kClDeepMaxLev + 1];
   int srows[kClDeepMaxLev + 1];   // frame rows of S_j
   int spitch[kClDeepMaxLev + 1];  // positions per frame row of S_j
-  int ssub[kClDeepMaxLev + 1];    // elements between the sub-bands of S_j
-  int soff[kClDeepMaxLev + 1];    // byte offset of S_j (slot 0); slots are sslot[j] elements apart
+  int soff[kClDeepMaxLev + 1];    // byte offset of S_j (slot 0); slots are sslot[j] elements apart,
+                                  // a frame is [row][position][sub-band][16 channels]
   int sslot[kClDeepMaxLev + 1];
   int roff[kClDeepMaxLev + 2];    // byte offset of R_j (j >= 2), rslot[j] floats per slot
   int rslot[kClDeepMaxLev + 2];
@@ -66,18 +66,17 @@ inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, 
   a.h[0] = (H + 1) / 2; a.w[0] = (W + 1) / 2;
   for (int j = 1; j <= a.nlev; ++j) { a.h[j] = (a.h[j - 1] + 1) / 2; a.w[j] = (a.w[j - 1] + 1) / 2; }
   long long off = 0;
-  for (int j = 0; j <= kClDeepMaxLev; ++j) { a.srows[j] = a.spitch[j] = a.ssub[j] = a.soff[j] = a.sslot[j] = 0; }
+  for (int j = 0; j <= kClDeepMaxLev; ++j) { a.srows[j] = a.spitch[j] = a.soff[j] = a.sslot[j] = 0; }
   for (int j = 1; j <= a.nlev; ++j) {
     a.srows[j] = (a.h[j] + 1) / 2 * 2 + 2 * HS;
     a.spitch[j] = (a.w[j] + 3) / 4 * 4 + 2 * HS;
-    a.ssub[j] = a.srows[j] * a.spitch[j] * kClGroup;
-    a.sslot[j] = 4 * a.ssub[j];
+    a.sslot[j] = a.srows[j] * a.spitch[j] * 4 * kClGroup;
     a.soff[j] = (int)off;
     off += (long long)ns * a.sslot[j] * elem_size;
     off = (off + 127) / 128 * 128;
     if (j == 1) a.zero_off = (int)off;
   }
-  if (a.srows[1] > 256 || a.spitch[1] > 256) return -1;     // one TMA box per sub-band
+  if (a.srows[1] > 256 || a.spitch[1] > 256) return -1;     // one TMA box per slot
   a.zero_bytes = (int)off - a.zero_off;
   for (int j = 0; j <= kClDeepMaxLev + 1; ++j) { a.roff[j] = 0; a.rslot[j] = 0; }
   for (int j = 2; j <= a.nlev; ++j) {
@@ -87,7 +86,7 @@ inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, 
   }
   off = (off + 127) / 128 * 128;
   a.woff = (int)off;
-  off += (long long)2 * 4 * (K * K + 1) * kClGroup * 4;
+  off += (long long)2 * (((4 * ((K * K + 1) * kClGroup * 4 + 32)) + 127) / 128 * 128);   // two buffers of four padded tap sets
   off = (off + 127) / 128 * 128;
   a.bar_off = (int)off;
   off += 128;
@@ -97,7 +96,7 @@ inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, 
   return off;
 }
 
-// s2: the second level's sub-bands from launch_cl_pyramid, (B, 4, h[1], w[1], C) in the layer's type
+// s2: the second level's sub-bands from launch_cl_pyramid, (B, h[1], w[1], 4, C) in the layer's type
 cudaError_t launch_cl_deep(const ClDeepArgs& a, int K, int dtype, const void* s2, const float* packed, float* rout,
                            int* status, cudaStream_t stream);
 

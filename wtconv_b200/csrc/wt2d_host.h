@@ -435,18 +435,17 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
     if (ly.L >= 2) {
       deep_ok = false;
       const int groups = cdiv(ly.C, kClGroup);
-      // one CTA of sixteen warps per SM: as many slots as keep its threads busy at the largest
-      // level (28 thread tiles of eight lanes fill seven warps) and leave two waves of CTAs
-      static const int cand[5] = {16, 8, 4, 2, 1};
-      for (int i = 0; i < 5 && !deep_ok; ++i) {
-        const int ns = cand[i];
-        const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, ly.H, ly.W, ly.K, ly.L, ly.elem_size, ns);
-        if (bytes < 0 || bytes > kSmemLimitBytes) continue;
-        const int tiles = cdiv(deep.deep.h[1], kClRH) * cdiv(deep.deep.w[1], kClCW);
-        const bool enough = (long long)cdiv(ly.B, ns) * groups >= 2 * 148 || ns == 1;
-        const bool useful = (ns == 1) || (long long)(ns / 2) * tiles * kClLanes < kClDeepThreads;
-        if (enough && useful) deep_ok = true;
-      }
+      // slots per CTA: as many as let two CTAs share an SM (their phases overlap) and still leave
+      // four CTAs per SM in the grid; failing that, the largest number that fits at all
+      static const int cand[4] = {8, 4, 2, 1};
+      for (int pass = 0; pass < 2 && !deep_ok; ++pass)
+        for (int i = 0; i < 4 && !deep_ok; ++i) {
+          const int ns = cand[i];
+          const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, ly.H, ly.W, ly.K, ly.L, ly.elem_size, ns);
+          if (bytes < 0 || bytes > (pass == 0 ? kSmemTwoPerSm : kSmemLimitBytes)) continue;
+          const bool enough = (long long)cdiv(ly.B, ns) * groups >= 4 * 148 || ns == 1;
+          if (enough) deep_ok = true;
+        }
       // the tensor map of the sub-band planes needs 16-byte row strides
       if ((ly.C * ly.elem_size) % 16 != 0) deep_ok = false;
     }
