@@ -9,6 +9,7 @@
 
 #include "../../include/wtconv_b200.h"
 #include "wt1d_host.h"
+#include "wt1d_warp.cuh"
 #include "wt2d_host.h"
 #include "wt2d_wgrad.cuh"
 #include "wt_aux.h"
@@ -494,6 +495,17 @@ int wtconv1d_forward(const void* x, void* y, const float* packed, int B, int C, 
     ly.xs[i] = x_strides ? x_strides[i] : dx[i];
     ly.ys[i] = y_strides ? y_strides[i] : dy[i];
     if (ly.xs[i] < 0 || ly.ys[i] < 0) return WTCONV_ERR_BAD_ARG;
+  }
+  if (wt1d_warp_supported(K, L, stride, ly.xs[2], ly.ys[2])) {
+    // time-contiguous signals, stride 1, up to four levels: the register-resident kernel
+    Warp1dArgs wa;
+    wa.x = x; wa.y = y; wa.packed = packed;
+    wa.B = B; wa.C = C; wa.N = N;
+    wa.wstride = packed_channel_floats(K, 1, L);
+    wa.nseg = 0; wa.nwarps = 0;
+    wa.xs0 = ly.xs[0]; wa.xs1 = ly.xs[1]; wa.ys0 = ly.ys[0]; wa.ys1 = ly.ys[1];
+    const cudaError_t e = launch_wt1d_warp(wa, K, L, dtype, static_cast<cudaStream_t>(stream));
+    if (e != cudaErrorNotSupported) return (int)e;     // more than 2^31 warps: the CTA-tile kernel below
   }
   Plan1d p;
   long long smem = 0;
