@@ -31,7 +31,7 @@ extern "C" {
 /* status codes (negative = argument errors, positive = cudaError_t) */
 #define WTCONV_OK 0
 #define WTCONV_ERR_BAD_ARG (-1)        /* null pointer, non-positive size, bad dtype code  */
-#define WTCONV_ERR_BAD_KERNEL_SIZE (-2)/* K is even or not compiled into this build         */
+#define WTCONV_ERR_BAD_KERNEL_SIZE (-2)/* K is even or larger than 29 (gradients: 1,3,5,7)    */
 #define WTCONV_ERR_BAD_LEVELS (-3)     /* wt_levels < 0 or beyond WTCONV_QUERY_MAX_LEVELS   */
 #define WTCONV_ERR_WORKSPACE (-4)      /* workspace missing or smaller than *_workspace_bytes */
 #define WTCONV_ERR_MISALIGNED (-5)     /* a pointer is not aligned to its element type      */
@@ -45,7 +45,7 @@ extern "C" {
 
 /* wtconv_query() selectors */
 #define WTCONV_QUERY_VERSION 0         /* ABI version, currently 1                          */
-#define WTCONV_QUERY_MAX_KERNEL_SIZE 1 /* largest odd K compiled in (odd K <= this work)    */
+#define WTCONV_QUERY_MAX_KERNEL_SIZE 1 /* largest K accepted: every odd K <= this works (29)   */
 #define WTCONV_QUERY_MAX_LEVELS 2      /* largest wt_levels accepted                        */
 #define WTCONV_QUERY_SM_ARCH 3         /* 100: built for sm_100a only                       */
 

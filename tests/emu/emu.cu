@@ -254,7 +254,7 @@ int emu_wtconv2d_forward(const void* x, void* y, const float* packed, int B, int
       case 3: run2d_k<3>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
       case 5: run2d_k<5>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
       case 7: run2d_k<7>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;
-      default: return WTCONV_ERR_BAD_KERNEL_SIZE;
+      default: run2d_k<0>(sg.plan, dt, xin, final_stage ? y : nullptr, packed, rin, rout); break;   // run-time kernel size
     }
   }
   return 0;
@@ -347,7 +347,7 @@ int emu_wtconv1d_forward(const void* x, void* y, const float* packed, int B, int
     case 3: run1d_k<3>(p, dtype, x, y, packed); break;
     case 5: run1d_k<5>(p, dtype, x, y, packed); break;
     case 7: run1d_k<7>(p, dtype, x, y, packed); break;
-    default: return WTCONV_ERR_BAD_KERNEL_SIZE;
+    default: run1d_k<0>(p, dtype, x, y, packed); break;   // run-time kernel size
   }
   return 0;
 }

@@ -219,3 +219,29 @@ def test_emulated_random_configurations(seed):
         assert max_err(out.numpy(), ref.numpy()) <= 1e-5, case
         chains.add((info[0], info[1], info[4], info[5]))
     assert len(chains) >= 3          # more than one kind of launch chain was exercised
+
+
+# Kernel sizes beyond the unrolled instances (1, 3, 5, 7) take the run-time-size instance of the
+# CTA-tile kernels; the reference's CUDA backend accepts odd sizes up to 29
+# (fast_wtconv/cuda_haar/haar_common.cuh:24-50), the pure-PyTorch reference any size.
+@pytest.mark.parametrize("case", [
+    (2, 3, 9, 2, (2, 3, 20, 17), 1, "nchw"), (2, 2, 11, 3, (1, 2, 40, 33), 1, "cl"), (2, 2, 29, 1, (1, 2, 30, 31), 1, "nchw"),
+    (2, 4, 9, 2, (1, 4, 16, 16), 2, "cl"), (2, 2, 15, 3, (1, 2, 90, 70), 1, "nchw"),
+    (1, 3, 9, 3, (2, 3, 100), 1, ""), (1, 2, 29, 2, (1, 2, 300), 3, ""), (1, 2, 13, 4, (1, 2, 257), 1, ""),
+], ids=lambda c: f"{c[0]}d-K{c[2]}-L{c[3]}-s{c[5]}{c[6]}")
+def test_emulated_run_time_kernel_size(case):
+    from oracle import wtconv_torch
+    nd, C, K, L, shape, stride, layout = case
+    params = wtconv_torch.random_params(C, K, L, ndim=nd, seed=K + L)
+    x = torch.randn(*shape, generator=torch.Generator().manual_seed(K))
+    packed = emu_lib.pack(params, nd, C, K, L)
+    p64 = {k: v.double() for k, v in params.items()}
+    if nd == 2:
+        xin = x.contiguous(memory_format=torch.channels_last) if layout == "cl" else x
+        y, _ = emu_lib.forward2d(xin, packed, K, L, stride=stride)
+        ref = wtconv_torch.wtconv2d_forward(x.double(), p64, stride=stride)
+    else:
+        y, _ = emu_lib.forward1d(x, packed, K, L, stride=stride)
+        ref = wtconv_torch.wtconv1d_forward(x.double(), p64, stride=stride)
+    assert tuple(y.shape) == tuple(ref.shape) and not torch.isnan(y).any()
+    assert max_err(y.numpy(), ref.numpy()) <= 1e-5

@@ -360,12 +360,12 @@ def test_c_abi_error_codes():
     xs = (ctypes.c_longlong * 4)(*x.stride())
     args = lambda K, L, dt: (x.data_ptr(), y.data_ptr(), packed.data_ptr(), None, 0, 1, 4, 8, 8, K, L, 1, dt, xs, xs, None)
     assert lib.wtconv2d_forward(*args(4, 1, 0)) == -2
-    assert lib.wtconv2d_forward(*args(9, 1, 0)) == -2
+    assert lib.wtconv2d_forward(*args(31, 1, 0)) == -2      # beyond the accepted range (odd sizes up to 29)
     assert lib.wtconv2d_forward(*args(5, -1, 0)) == -3
     assert lib.wtconv2d_forward(*args(5, 1, 7)) == -1
     assert lib.wtconv2d_forward(None, y.data_ptr(), packed.data_ptr(), None, 0, 1, 4, 8, 8, 5, 1, 1, 0, xs, xs, None) == -1
     assert lib.wtconv2d_forward(*args(5, 1, 0)) == 0
-    m = wtconv_b200.WTConv2d(4, 4, kernel_size=9, wt_levels=1).to(dev)
+    m = wtconv_b200.WTConv2d(4, 4, kernel_size=31, wt_levels=1).to(dev)
     with torch.no_grad(), pytest.raises(ValueError):
         m(x)
     torch.cuda.synchronize()
@@ -465,3 +465,27 @@ def test_parameter_gradients_1d(shape, L, K, stride):
     for n, r in zip(names, refs[1:]):
         err = max_err(got[n].grad.cpu().numpy(), r.numpy())
         assert err <= 1e-4, f"{n}: {err:.3e}"
+
+
+# Kernel sizes without an unrolled instance (odd, 9 .. 29): the run-time-size CTA-tile kernels.
+@pytest.mark.parametrize("case", [
+    (2, 8, 9, 3, (2, 8, 40, 37), 1, "cl", torch.float32), (2, 6, 11, 2, (2, 6, 56, 56), 1, "nchw", torch.float32),
+    (2, 4, 29, 1, (1, 4, 64, 48), 1, "cl", torch.float32), (2, 16, 9, 2, (2, 16, 28, 28), 2, "cl", torch.bfloat16),
+    (2, 4, 13, 4, (1, 4, 150, 120), 1, "nchw", torch.float32),
+    (1, 6, 9, 3, (2, 6, 1000), 1, "", torch.float32), (1, 4, 29, 2, (2, 4, 4097), 2, "", torch.float32),
+    (1, 8, 15, 4, (2, 8, 4096), 1, "", torch.bfloat16),
+], ids=lambda c: f"{c[0]}d-K{c[2]}-L{c[3]}-s{c[5]}{c[6]}-{str(c[7])[6:]}")
+def test_run_time_kernel_size(case):
+    dev = _cuda()
+    nd, C, K, L, shape, stride, layout, dtype = case
+    params = wtconv_torch.random_params(C, K, L, ndim=nd, seed=K + L)
+    x = torch.randn(*shape, generator=torch.Generator().manual_seed(K))
+    m = _module(nd, C, K, L, stride, True, params, dtype, dev)
+    xt = x.to(dev).to(dtype)
+    if layout == "cl":
+        xt = xt.contiguous(memory_format=torch.channels_last)
+    with torch.no_grad():
+        out = m(xt).float().cpu()
+    ref = _oracle(nd, x, params, stride, torch.float64 if dtype == torch.float32 else dtype).float()
+    assert tuple(out.shape) == tuple(ref.shape)
+    assert max_err(out.numpy(), ref.numpy()) <= TOL[dtype]

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
 def test_host_only_entry_points():
     L = _lib()
     lib = L.load()
-    assert lib.wtconv_query(0) == 1 and lib.wtconv_query(1) == 7 and lib.wtconv_query(3) == 100
+    assert lib.wtconv_query(0) == 1 and lib.wtconv_query(1) == 29 and lib.wtconv_query(3) == 100
     # 2-D: per-channel block (28 floats per tap set, 1 + 4*5 sets) + channels-last copy (26 x 16 per set and group)
     assert lib.wtconv_packed_param_floats(2, 96, 5, 5) == 96 * 28 * 21 + 6 * 21 * 26 * 16
     assert lib.wtconv_packed_param_floats(1, 64, 5, 4) == 64 * 8 * 9

@@ -20,7 +20,7 @@ namespace {
 
 inline bool valid_dtype(int d) { return d == WTCONV_F32 || d == WTCONV_BF16 || d == WTCONV_F16; }
 inline int elem_size(int d) { return d == WTCONV_F32 ? 4 : 2; }
-inline bool built_k(int K) { return K == 1 || K == 3 || K == 5 || K == 7; }
+inline bool unrolled_k(int K) { return K == 1 || K == 3 || K == 5 || K == 7; }   // other odd sizes up to kMaxK take the run-time instance
 inline int ptr_align(const void* p) {
   const uintptr_t a = reinterpret_cast<uintptr_t>(p);
   int al = 16;
@@ -34,7 +34,8 @@ cudaError_t launch_wt2d(const Plan2d& p, int dtype, const void* x, void* y, cons
     case 1: return launch_wt2d_k<1>(p, dtype, x, y, packed, rin, rout, smem, st);
     case 3: return launch_wt2d_k<3>(p, dtype, x, y, packed, rin, rout, smem, st);
     case 5: return launch_wt2d_k<5>(p, dtype, x, y, packed, rin, rout, smem, st);
-    default: return launch_wt2d_k<7>(p, dtype, x, y, packed, rin, rout, smem, st);
+    case 7: return launch_wt2d_k<7>(p, dtype, x, y, packed, rin, rout, smem, st);
+    default: return launch_wt2d_k<0>(p, dtype, x, y, packed, rin, rout, smem, st);
   }
 }
 
@@ -44,7 +45,8 @@ cudaError_t launch_wt1d(const Plan1d& p, int dtype, const void* x, void* y, cons
     case 1: return launch_wt1d_k<1>(p, dtype, x, y, packed, smem, st);
     case 3: return launch_wt1d_k<3>(p, dtype, x, y, packed, smem, st);
     case 5: return launch_wt1d_k<5>(p, dtype, x, y, packed, smem, st);
-    default: return launch_wt1d_k<7>(p, dtype, x, y, packed, smem, st);
+    case 7: return launch_wt1d_k<7>(p, dtype, x, y, packed, smem, st);
+    default: return launch_wt1d_k<0>(p, dtype, x, y, packed, smem, st);
   }
 }
 
@@ -59,7 +61,7 @@ int* wait_status_address() {
 
 int check_common(int C, int K, int L, int dtype) {
   if (C <= 0 || !valid_dtype(dtype)) return WTCONV_ERR_BAD_ARG;
-  if (K < 1 || (K % 2) == 0 || !built_k(K)) return WTCONV_ERR_BAD_KERNEL_SIZE;
+  if (K < 1 || (K % 2) == 0 || K > kMaxK) return WTCONV_ERR_BAD_KERNEL_SIZE;
   if (L < 0 || L > kMaxLevels) return WTCONV_ERR_BAD_LEVELS;
   return WTCONV_OK;
 }
@@ -130,7 +132,7 @@ const char* wtconv_status_string(int status) {
   switch (status) {
     case WTCONV_OK: return "ok";
     case WTCONV_ERR_BAD_ARG: return "invalid argument (null pointer, non-positive size, negative stride or unknown dtype code)";
-    case WTCONV_ERR_BAD_KERNEL_SIZE: return "kernel_size must be odd and one of the sizes compiled into this build (1, 3, 5, 7)";
+    case WTCONV_ERR_BAD_KERNEL_SIZE: return "kernel_size must be odd and at most 29 (parameter gradients: 1, 3, 5 or 7)";
     case WTCONV_ERR_BAD_LEVELS: return "wt_levels is negative or larger than this build supports";
     case WTCONV_ERR_WORKSPACE: return "workspace pointer missing or smaller than wtconv2d_workspace_bytes()";
     case WTCONV_ERR_MISALIGNED: return "a tensor pointer is not aligned to its element size";
@@ -249,6 +251,7 @@ int wtconv2d_weight_grad_stats(const void* x, const void* gy, const float* x_pyr
   if (!x || !gy || !stats || (L > 0 && (!x_pyramid || !g_pyramid))) return WTCONV_ERR_BAD_ARG;
   const int st = check_common(C, K, L, dtype);
   if (st) return st;
+  if (!unrolled_k(K)) return WTCONV_ERR_BAD_KERNEL_SIZE;      // the correlation kernels exist for 1, 3, 5, 7 only
   if (B <= 0 || H <= 0 || W <= 0) return WTCONV_ERR_BAD_ARG;
   if ((long long)B * C * H * W >= (1LL << 40) || (long long)C * H * W >= (1LL << 31)) return WTCONV_ERR_TOO_LARGE;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);

@@ -43,8 +43,17 @@ constexpr int kTile1d = 8;   // level positions per item
 
 // K-tap cross-correlation of TW consecutive outputs; `src` is the first sample
 // of the (TW+K-1)-sample window, 16-byte aligned.
+// K = 0 is the generic instance: the kernel size `kdyn` is a run-time value (any odd size up to kMaxK).
 template <int K, int TW>
-WT_HD void conv_row(const float* __restrict__ src, const float* __restrict__ wts, float (&acc)[TW]) {
+WT_HD void conv_row(const float* __restrict__ src, const float* __restrict__ wts, float (&acc)[TW], int kdyn) {
+  if constexpr (K == 0) {
+    for (int j = 0; j < kdyn; ++j) {
+      const float w = wts[j];
+#pragma unroll
+      for (int o = 0; o < TW; ++o) acc[o] = fmaf(w, src[o + j], acc[o]);
+    }
+  } else {
+  (void)kdyn;
   constexpr int WIN = TW + K - 1;
   constexpr int NV = (WIN + 3) / 4;
   constexpr int NW = (K + 3) / 4;
@@ -63,6 +72,7 @@ WT_HD void conv_row(const float* __restrict__ src, const float* __restrict__ wts
   for (int j = 0; j < K; ++j)
 #pragma unroll
     for (int o = 0; o < TW; ++o) acc[o] = fmaf(w[j], row[o + j], acc[o]);
+  }
 }
 
 struct Smem1d {
@@ -86,8 +96,8 @@ WT_HD void level_item_1d(const Plan1d& p, const Smem1d& sm, int j, int g, int ix
   float lo[TW], hi[TW];
 #pragma unroll
   for (int o = 0; o < TW; ++o) { lo[o] = 0.f; hi[o] = 0.f; }
-  conv_row<K, TW>(sm.sub(j, g, 0) + wx, sm.taps(g, j, 0), lo);
-  conv_row<K, TW>(sm.sub(j, g, 1) + wx, sm.taps(g, j, 1), hi);
+  conv_row<K, TW>(sm.sub(j, g, 0) + wx, sm.taps(g, j, 0), lo, p.K);
+  conv_row<K, TW>(sm.sub(j, g, 1) + wx, sm.taps(g, j, 1), hi, p.K);
   if (has_r) {
     const float* rj = sm.rec(j, g) + ix * TW;
 #pragma unroll
@@ -217,7 +227,7 @@ WT_HD void wt1d_cta(const Plan1d& p, const T* __restrict__ x, T* __restrict__ y,
             const bool ok = px >= 0 && px < Nj && sx >= 0 && sx + 1 < sp;
             const int cx = imin(imax(sx, 0), sp - 2);
             float a, b;
-            if ((K / 2) % 2 == 0) load2(s0 + (cx & ~1), a, b);
+            if (K != 0 && (K / 2) % 2 == 0) load2(s0 + (cx & ~1), a, b);
             else { a = s0[cx]; b = s0[cx + 1]; }
             lo[k] = ok ? a + b : 0.f;
             hi[k] = ok ? a - b : 0.f;
@@ -281,10 +291,10 @@ WT_HD void wt1d_cta(const Plan1d& p, const T* __restrict__ x, T* __restrict__ y,
         for (int o = 0; o < 2 * TW; ++o) acc[o] = 0.f;
       }
       const float* wts = sm.taps(g, 0, 0);
-      const float bias = wts[K];
+      const float bias = wts[p.K];
 #pragma unroll
       for (int o = 0; o < 2 * TW; ++o) acc[o] += bias;
-      conv_row<K, 2 * TW>(sm.x0(g) + wx0 + ix * 2 * TW, wts, acc);
+      conv_row<K, 2 * TW>(sm.x0(g) + wx0 + ix * 2 * TW, wts, acc, p.K);
       const int nvalid = n0 - ix * 2 * TW;
       if (p.out_stride == 1) {
         store_run16<T>(yb + (size_t)g * p.ys[1] + (size_t)(t0 + ix * 2 * TW) * p.ys[2], p.ys[2], acc, nvalid);

@@ -79,9 +79,23 @@ WT_HD void load2(const H* p, float& a, float& b) {
 // applied to all output rows it contributes to, so each loaded element feeds
 // about K*min(K,TH)*TW/(TW+K-1) FMAs.
 // ---------------------------------------------------------------------------
+// K = 0 is the generic instance: the kernel size `kdyn` is a run-time value, taps and window
+// elements are read one by one (any odd size up to kMaxK; slower than the unrolled sizes).
 template <int K, int TH, int TW, typename ST>
 WT_HD void conv_tile(const ST* __restrict__ src, int pitch, const float* __restrict__ wts,
-                     float (&acc)[TH][TW]) {
+                     float (&acc)[TH][TW], int kdyn) {
+  if constexpr (K == 0) {
+    for (int i = 0; i < kdyn; ++i)
+      for (int j = 0; j < kdyn; ++j) {
+        const float w = wts[i * kdyn + j];
+#pragma unroll
+        for (int oh = 0; oh < TH; ++oh)
+#pragma unroll
+          for (int ow = 0; ow < TW; ++ow)
+            acc[oh][ow] = fmaf(w, Elem<ST>::to_f(src[(oh + i) * pitch + ow + j]), acc[oh][ow]);
+      }
+  } else {
+  (void)kdyn;
   constexpr int WIN = TW + K - 1;
   constexpr int NV = (WIN + 3) / 4;
   constexpr int NW = (K * K + 3) / 4;
@@ -111,6 +125,7 @@ WT_HD void conv_tile(const ST* __restrict__ src, int pitch, const float* __restr
         }
       }
     }
+  }
   }
 }
 
@@ -186,7 +201,7 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, in
       for (int i = 0; i < TH; ++i)
 #pragma unroll
         for (int q = 0; q < TW; ++q) y[i][q] = 0.f;
-      conv_tile<K, TH, TW, float>(sb + s * sstep, pitch, tp + s * p.tapset, y);
+      conv_tile<K, TH, TW, float>(sb + s * sstep, pitch, tp + s * p.tapset, y, p.K);
       const float fy = (s & 1) ? -1.f : 1.f, fx = (s & 2) ? -1.f : 1.f, fxy = fx * fy;
 #pragma unroll
       for (int i = 0; i < TH; ++i)
@@ -202,12 +217,12 @@ WT_HD void top_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, in
   if (FUSE_BASE) {
     const int pitch = p.pitch[0];
     const float* wts = sm.taps(g, 0, 0);
-    const float bias = wts[K * K];
+    const float bias = wts[p.K * p.K];
 #pragma unroll
     for (int i = 0; i < 2 * TH; ++i)
 #pragma unroll
       for (int q = 0; q < 2 * TW; ++q) acc[i][q] += bias;
-    conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc);
+    conv_tile<K, 2 * TH, 2 * TW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc, p.K);
     if (p.direct_store) {
       // finished pixels -> y: `ytile` is the tile's first pixel of the group's first channel
       const int ys2 = (int)p.ys[2], ys3 = (int)p.ys[3];
@@ -270,13 +285,13 @@ WT_HD void base_item(const Plan2d& p, const Smem2d& sm, int g, int iy, int ix, i
   constexpr int BH = 4, BW = 8;
   const int pitch = p.pitch[0];
   const float* wts = sm.taps(g, 0, 0);
-  const float bias = wts[K * K];
+  const float bias = wts[p.K * p.K];
   float acc[BH][BW];
 #pragma unroll
   for (int i = 0; i < BH; ++i)
 #pragma unroll
     for (int q = 0; q < BW; ++q) acc[i][q] = bias;
-  conv_tile<K, BH, BW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc);
+  conv_tile<K, BH, BW, XT>(sm.x0<XT>(g) + wy0 * pitch + wx0, pitch, wts, acc, p.K);
   T* o = out_tile + g * p.oplane + (iy * BH) * p.opitch + ix * BW;
 #pragma unroll
   for (int i = 0; i < BH; ++i) {
@@ -294,7 +309,7 @@ WT_HD void deep_item(const Plan2d& p, const Smem2d& sm, int j, int g, int s, int
   for (int i = 0; i < TH; ++i)
 #pragma unroll
     for (int q = 0; q < 4; ++q) y[i][q] = 0.f;
-  conv_tile<K, TH, 4, float>(sm.sub(j, g, s) + wy * pitch + wx, pitch, sm.taps(g, j, s), y);
+  conv_tile<K, TH, 4, float>(sm.sub(j, g, s) + wy * pitch + wx, pitch, sm.taps(g, j, s), y, p.K);
   float* o = sm.ybuf(g, s) + (iy * TH) * p.ypitch + ix * 4;
 #pragma unroll
   for (int i = 0; i < TH; ++i) store4(o + i * p.ypitch, y[i][0], y[i][1], y[i][2], y[i][3]);
@@ -553,7 +568,7 @@ WT_HD void analysis_level(const Plan2d& p, const Smem2d& sm, int j, int oy, int 
         const bool ok = rowok && px >= 0 && px < Wj && sx >= 0 && sx + 1 < sp;
         const int cx = imin(imax(sx, 0), sp - 2);
         float a0, a1, b0, b1;
-        if ((K / 2) % 2 == 0) {                    // even radius: source column pairs are aligned
+        if (K != 0 && (K / 2) % 2 == 0) {          // even radius: source column pairs are aligned
           load2(s0 + (cx & ~1), a0, a1);
           load2(s0 + sp + (cx & ~1), b0, b1);
         } else {

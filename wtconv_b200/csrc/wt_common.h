@@ -32,7 +32,7 @@ namespace wt {
 
 constexpr int kMaxFused = 8;    // wavelet levels one launch can fuse on chip
 constexpr int kMaxLevels = 16;  // wt_levels accepted by the entry points
-constexpr int kMaxK = 7;        // largest odd kernel size compiled in
+constexpr int kMaxK = 29;       // largest odd kernel size accepted (1, 3, 5, 7 are unrolled instances)
 
 WT_HD int imin(int a, int b) { return a < b ? a : b; }
 WT_HD int imax(int a, int b) { return a > b ? a : b; }
