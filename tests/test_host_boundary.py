@@ -73,6 +73,8 @@ def test_launch_chains_of_the_benchmark_shapes():
     assert count(128, 768, 7, 5, 2, 1, False) == 1          # NCHW: one whole-plane CTA-tile stage
     assert count(128, 96, 56, 5, 5, 1, False) == 1          # NCHW: the 56x56 pyramid still fits on chip
     assert count(2, 256, 512, 5, 5, 1, False) >= 4          # 512x512: reductions and a chain of tiled stages
+    # channels-last 512x512: two low-pass launches, pyramid, deep stage (level 5), level stages 4, 3, 2, 1
+    assert count(2, 256, 512, 5, 5, 1, True) == 8
     assert count(128, 768, 7, 3, 2, 1, True) == 1           # K = 3 has no register-level instance
     assert count(4, 16, 7, 5, 2, 0, True, stride=2) == 1    # strided output: CTA-tile stage
     n = ctypes.c_int(0)

@@ -417,9 +417,15 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
       case 4:   // input: the sub-bands of level 2 in the layer's type
         e = launch_cl_deep(sg.deep, ly.K, dtype, xin, packed, rout, wait_status, cs);
         break;
-      case 5: {
-        const int xv = (ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0;
-        e = launch_cl_pyramid(dtype, x, ly.xs, xv, ly.B, ly.C, ly.H, ly.W, rout, cs);
+      case 5:     // sub-bands two levels below the plane set read (layer input or a dense low-pass plane set)
+      case 6: {   // low-pass planes one and two levels below it
+        const long long dense[4] = {(long long)sg.cl.H * sg.cl.W * ly.C, 1, (long long)sg.cl.W * ly.C, ly.C};
+        const long long* s = from_x ? ly.xs : dense;
+        const int xv = from_x ? ((ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0)
+                              : ((ly.C % 2 == 0) ? 1 : 0);
+        if (sg.kind == 5) e = launch_cl_pyramid(dtype, xin, s, xv, ly.B, ly.C, sg.cl.H, sg.cl.W, rout, cs);
+        else e = launch_cl_lowpass(dtype, xin, s, xv, ly.B, ly.C, sg.cl.H, sg.cl.W, rout,
+                                   sg.rin_off < 0 ? nullptr : static_cast<void*>(ws + sg.rin_off), cs);
         break;
       }
       default:

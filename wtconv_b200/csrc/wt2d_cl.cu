@@ -145,7 +145,34 @@ cudaError_t launch_pyramid_t(const void* x, const long long* xs, int x_vec, int 
   return cudaGetLastError();
 }
 
+template <typename T>
+cudaError_t launch_lowpass_t(const void* x, const long long* xs, int x_vec, int B, int C, int H, int W, void* p1, void* p2,
+                             cudaStream_t stream) {
+  ClLowpassArgs a;
+  a.x = x;
+  for (int i = 0; i < 4; ++i) a.xs[i] = xs[i];
+  a.x_vec = x_vec;
+  a.B = B; a.C = C; a.H = H; a.W = W;
+  a.h1 = (H + 1) / 2; a.w1 = (W + 1) / 2;
+  a.h2 = (a.h1 + 1) / 2; a.w2 = (a.w1 + 1) / 2;
+  a.p1 = p1; a.p2 = p2;
+  a.total = (long long)B * a.h2 * a.w2 * ((C + 1) / 2);
+  const long long want = (a.total + 255) / 256;
+  const int blocks = (int)(want > 148 * 64 ? 148 * 64 : want);
+  wt2d_cl_lowpass_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
 }  // namespace
+
+cudaError_t launch_cl_lowpass(int dtype, const void* x, const long long* xs, int x_vec, int B, int C, int H, int W,
+                              void* p1, void* p2, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return launch_lowpass_t<float>(x, xs, x_vec, B, C, H, W, p1, p2, st);
+    case 1: return launch_lowpass_t<__nv_bfloat16>(x, xs, x_vec, B, C, H, W, p1, p2, st);
+    default: return launch_lowpass_t<__half>(x, xs, x_vec, B, C, H, W, p1, p2, st);
+  }
+}
 
 cudaError_t launch_cl_pyramid(int dtype, const void* x, const long long* xs, int x_vec, int B, int C, int H, int W,
                               void* s2, cudaStream_t st) {

@@ -615,6 +615,71 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 }
 
 // ---------------------------------------------------------------------------
+// Low-pass planes for the level stages below the top one (large planes only): a plane set
+// (the layer input, or a low-pass plane set written by an earlier launch of this kernel) ->
+// the low-pass planes one and, optionally, two levels down, dense channels-last in the input's
+// type and at the reference's scale (the reference also keeps its low-pass planes in that type,
+// wtconv2d.py:55).  One thread owns one channel pair of one 4 x 4 pixel block.
+// ---------------------------------------------------------------------------
+struct ClLowpassArgs {
+  const void* x;
+  long long xs[4];      // strides in elements: n, c (= 1), h, w
+  int x_vec;            // 1: channel pairs may be loaded as one word
+  int B, C, H, W;
+  int h1, w1, h2, w2;   // sizes one and two levels down
+  void* p1;             // (B, h1, w1, C)
+  void* p2;             // (B, h2, w2, C) or null
+  long long total;      // B * h2 * w2 * ceil(C/2)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) wt2d_cl_lowpass_kernel(const __grid_constant__ ClLowpassArgs a) {
+#ifdef __CUDA_ARCH__
+  const int P = (a.C + 1) / 2;
+  const bool cpair = a.x_vec != 0;
+  const bool even_c = (a.C & 1) == 0;
+  for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < a.total; id += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(id % P);
+    long long t = id / P;
+    const int f = (int)(t % a.w2);
+    t /= a.w2;
+    const int k = (int)(t % a.h2);
+    const int n = (int)(t / a.h2);
+    const int c = 2 * p;
+    const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
+    const bool both = (c + 1 < a.C);
+    typename ClPair<T>::raw_t r[4][4];
+#pragma unroll
+    for (int yy = 0; yy < 4; ++yy)
+#pragma unroll
+      for (int xx = 0; xx < 4; ++xx)
+        r[yy][xx] = ClPair<T>::load_global(p0 + yy * a.xs[2] + xx * a.xs[3], 4 * k + yy < a.H && 4 * f + xx < a.W, cpair && both, both);
+    float2 l[2][2];
+#pragma unroll
+    for (int by = 0; by < 2; ++by)
+#pragma unroll
+      for (int bx = 0; bx < 2; ++bx) {
+        const float2 va = ClPair<T>::widen(r[2 * by][2 * bx]), vb = ClPair<T>::widen(r[2 * by][2 * bx + 1]);
+        const float2 vc = ClPair<T>::widen(r[2 * by + 1][2 * bx]), vd = ClPair<T>::widen(r[2 * by + 1][2 * bx + 1]);
+        l[by][bx] = __fmul2_rn(cl_add2(cl_add2(va, vb), cl_add2(vc, vd)), make_float2(0.5f, 0.5f));
+        const int y1 = 2 * k + by, x1 = 2 * f + bx;
+        if (y1 < a.h1 && x1 < a.w1) {
+          T* d = static_cast<T*>(a.p1) + (((size_t)n * a.h1 + y1) * a.w1 + x1) * a.C + c;
+          if (both && even_c) ClPair<T>::store(d, l[by][bx]);
+          else { d[0] = Elem<T>::from_f(l[by][bx].x); if (both) d[1] = Elem<T>::from_f(l[by][bx].y); }
+        }
+      }
+    if (a.p2) {
+      const float2 ll = __fmul2_rn(cl_add2(cl_add2(l[0][0], l[0][1]), cl_add2(l[1][0], l[1][1])), make_float2(0.5f, 0.5f));
+      T* d = static_cast<T*>(a.p2) + (((size_t)n * a.h2 + k) * a.w2 + f) * a.C + c;
+      if (both && even_c) ClPair<T>::store(d, ll);
+      else { d[0] = Elem<T>::from_f(ll.x); if (both) d[1] = Elem<T>::from_f(ll.y); }
+    }
+  }
+#endif
+}
+
+// ---------------------------------------------------------------------------
 // Deep stage: every level from the second one down, whole planes on chip.
 //
 // A CTA owns NS plane slots (sample, 16-channel group).  The sub-bands of the second level
@@ -624,7 +689,8 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 // deepest level first, and the reconstruction that the top level adds to its low-pass result
 // (wtconv2d.py:64-76) leaves as fp32 channels-last planes.
 //
-// On-chip level j = 1..nlev is layer level j+1.  S_j: frame of (h_j + 2*HS) x (w_j + 2*HS)
+// On-chip level j = 1..nlev is layer level lvl0+j+1 (lvl0 = 0 when the stage starts from the layer
+// input's second level).  S_j: frame of (h_j + 2*HS) x (w_j + 2*HS)
 // positions (rounded up to whole thread tiles) with a zero border, stored
 // [row][column][sub-band][16 channels] in the input's type at the reference's scale;
 // R_j: fp32 reconstruction of level j, h_{j-1} x w_{j-1} positions of 16 channels.
@@ -754,7 +820,7 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     cl_mbar_expect_tx(&bars[buf], 4u * kSetBytes);
     for (int sb = 0; sb < 4; ++sb)
       cl_bulk_load(wbuf + (size_t)buf * kClDeepLevelBytes + (size_t)sb * kClDeepSetPitch,
-                   wsrc + (size_t)(1 + 4 * j + sb) * (TAPS * kClGroup), kSetBytes, &bars[buf]);
+                   wsrc + (size_t)(1 + 4 * (a.lvl0 + j) + sb) * (TAPS * kClGroup), kSetBytes, &bars[buf]);
   };
 
   if (tid == 0) {

@@ -37,6 +37,7 @@ struct ClDeepArgs {
   int B, C, H, W;                 // layer input
   int nlev;                       // levels on chip (layer levels 2 .. nlev+1)
   int nlevels;                    // wavelet levels of the layer
+  int lvl0;                       // layer levels above the plane set this stage starts from (0: the layer input)
   int ns;                         // plane slots per CTA
   int h[kClDeepMaxLev + 1];       // h[0], w[0]: plane of LL_1; h[j] = ceil(h[j-1]/2)
   int w[kClDeepMaxLev + 1];
@@ -60,7 +61,7 @@ struct ClDeepArgs {
 // needs in bytes, or -1 when the plane set cannot be handled.
 inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, int L, int elem_size, int ns) {
   const int HS = K / 2;
-  a.B = B; a.C = C; a.H = H; a.W = W; a.ns = ns; a.nlevels = L;
+  a.B = B; a.C = C; a.H = H; a.W = W; a.ns = ns; a.nlevels = L; a.lvl0 = 0;
   a.nlev = L - 1;
   if (a.nlev < 1 || a.nlev > kClDeepMaxLev || ns > 64) return -1;
   a.h[0] = (H + 1) / 2; a.w[0] = (W + 1) / 2;
@@ -99,6 +100,11 @@ inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, 
 // s2: the second level's sub-bands from launch_cl_pyramid, (B, h[1], w[1], 4, C) in the layer's type
 cudaError_t launch_cl_deep(const ClDeepArgs& a, int K, int dtype, const void* s2, const float* packed, float* rout,
                            int* status, cudaStream_t stream);
+
+// plane set (channels-last, strides xs in elements) -> low-pass planes one (p1) and two (p2, may be
+// null) levels down, dense channels-last in the same type
+cudaError_t launch_cl_lowpass(int dtype, const void* x, const long long* xs, int x_vec, int B, int C, int H, int W,
+                              void* p1, void* p2, cudaStream_t stream);
 
 // x (channels-last, strides xs in elements) -> s2
 cudaError_t launch_cl_pyramid(int dtype, const void* x, const long long* xs, int x_vec, int B, int C, int H, int W,

@@ -217,7 +217,9 @@ inline long long plan_quad(QuadPlane& a, int B, int C, int K, int L, int q, int 
 struct Stage2d {
   // 0: CTA-tile kernel (plan), 1: register-resident small-plane kernel (reg),
   // 2: four-warp 14 x 14 level kernel (quad), 3: channels-last level stage (cl),
-  // 4: channels-last deep stage (deep), 5: channels-last sub-band pyramid of the layer input
+  // 4: channels-last deep stage (deep), 5: channels-last sub-band pyramid, 6: channels-last low-pass
+  // planes (5 and 6 read the layer input or a low-pass plane set of cl.H x cl.W; 6 writes one
+  // level down to rout_off and, if rin_off >= 0, two levels down there)
   int kind = 0;
   RegPlane reg;
   QuadPlane quad;
@@ -430,49 +432,81 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // planes on chip) for the levels below the top one, then the level stage of the top level with
   // the base path.
   if (use_cl && ly.L >= 1 && (ly.H > 16 || ly.W > 16)) {
+    // The level stage takes the top nl levels one launch each (the first nl-1 of them read low-pass
+    // planes that a reduction kernel writes); the deep stage takes the rest, whose sub-bands must
+    // fit on chip.  nl is as small as the shared memory allows: 1 for planes up to about 64 x 64.
+    const bool tma_rows = (ly.C * ly.elem_size) % 16 == 0;     // dense planes in scratch feed tensor maps too
+    const int groups = cdiv(ly.C, kClGroup);
     Stage2d deep;
-    bool deep_ok = true;
-    if (ly.L >= 2) {
-      deep_ok = false;
-      const int groups = cdiv(ly.C, kClGroup);
+    int nl = 0;
+    for (int n = 1; n <= ly.L && !nl; ++n) {
+      const int rest = ly.L - n;                               // levels left to the deep stage
+      if (rest == 0) { nl = n; break; }
+      if (!tma_rows) break;
       // slots per CTA: as many as let two CTAs share an SM (their phases overlap) and still leave
       // four CTAs per SM in the grid; failing that, the largest number that fits at all
       static const int cand[4] = {8, 4, 2, 1};
-      for (int pass = 0; pass < 2 && !deep_ok; ++pass)
-        for (int i = 0; i < 4 && !deep_ok; ++i) {
+      for (int pass = 0; pass < 2 && !nl; ++pass)
+        for (int i = 0; i < 4 && !nl; ++i) {
           const int ns = cand[i];
-          const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, ly.H, ly.W, ly.K, ly.L, ly.elem_size, ns);
+          const long long bytes = plan_cl_deep(deep.deep, ly.B, ly.C, Hl[n - 1], Wl[n - 1], ly.K, rest + 1, ly.elem_size, ns);
           if (bytes < 0 || bytes > (pass == 0 ? kSmemTwoPerSm : kSmemLimitBytes)) continue;
           const bool enough = (long long)cdiv(ly.B, ns) * groups >= 4 * 148 || ns == 1;
-          if (enough) deep_ok = true;
+          if (enough) nl = n;
         }
-      // the tensor map of the sub-band planes needs 16-byte row strides
-      if ((ly.C * ly.elem_size) % 16 != 0) deep_ok = false;
     }
-    if (deep_ok) {
-      if (ly.L >= 2) {
-        const long long n1 = ((long long)ly.B * Hl[1] * Wl[1] * ly.C + 3) / 4 * 4;    // floats of the level-1 reconstruction
-        const long long s2_elems = (long long)ly.B * 4 * Hl[2] * Wl[2] * ly.C;
+    if (nl > 1 && !tma_rows) nl = 0;
+    if (nl) {
+      const bool has_deep = ly.L > nl;
+      auto align4 = [](long long v) { return (v + 3) / 4 * 4; };
+      auto elems_as_floats = [&](long long elems) { return align4((elems * ly.elem_size + 3) / 4); };
+      // scratch: reconstructions read by levels 1..nl (fp32), low-pass planes 1..nl-1 and the deep
+      // stage's sub-bands (the layer's type)
+      std::vector<long long> roff(nl + 1, -1), poff(nl, -1);
+      long long off = 0;
+      for (int jl = 1; jl <= nl; ++jl)
+        if (jl < nl || has_deep) { roff[jl] = off; off += align4((long long)ly.B * Hl[jl] * Wl[jl] * ly.C); }
+      for (int jl = 1; jl < nl; ++jl) { poff[jl] = off; off += elems_as_floats((long long)ly.B * Hl[jl] * Wl[jl] * ly.C); }
+      long long soff = -1;
+      if (has_deep) { soff = off; off += elems_as_floats((long long)ly.B * 4 * Hl[nl + 1] * Wl[nl + 1] * ly.C); }
+      ch.scratch_floats = off;
+      // low-pass planes, two levels per launch
+      for (int jl = 1; jl < nl; jl += 2) {
+        Stage2d lp;
+        lp.kind = 6;
+        lp.cl.H = Hl[jl - 1]; lp.cl.W = Wl[jl - 1];
+        lp.xin_off = (jl == 1) ? -1 : poff[jl - 1];
+        lp.rout_off = poff[jl];
+        lp.rin_off = (jl + 1 < nl) ? poff[jl + 1] : -1;        // second output, if wanted
+        lp.smem_bytes = 0;
+        ch.stages.push_back(lp);
+      }
+      if (has_deep) {
         Stage2d pyr;
         pyr.kind = 5;
-        pyr.xin_off = -1; pyr.rin_off = -1; pyr.rout_off = n1;      // sub-bands of level 2, in the layer's type
+        pyr.cl.H = Hl[nl - 1]; pyr.cl.W = Wl[nl - 1];
+        pyr.xin_off = (nl == 1) ? -1 : poff[nl - 1];
+        pyr.rin_off = -1; pyr.rout_off = soff;                 // sub-bands of level nl+1, in the layer's type
         pyr.smem_bytes = 0;
         ch.stages.push_back(pyr);
         deep.kind = 4;
         deep.deep.cl_off = cl_param_offset(ly.C, ly.K, ly.L);
-        deep.xin_off = n1; deep.rin_off = -1; deep.rout_off = 0;
+        deep.deep.nlevels = ly.L;
+        deep.deep.lvl0 = nl - 1;
+        deep.xin_off = soff; deep.rin_off = -1; deep.rout_off = roff[nl];
         deep.smem_bytes = deep.deep.smem_bytes;
         ch.stages.push_back(deep);
-        ch.scratch_floats = n1 + ((s2_elems * ly.elem_size + 3) / 4 + 3) / 4 * 4;
       }
-      Stage2d st;
-      st.kind = 3;
-      plan_cl_level(st.cl, ly, 0, ly.H, ly.W, true, 0.5f);
-      st.smem_bytes = 0;
-      st.xin_off = -1;
-      st.rin_off = (ly.L >= 2) ? 0 : -1;
-      st.rout_off = -1;
-      ch.stages.push_back(st);
+      for (int jl = nl; jl >= 1; --jl) {
+        Stage2d st;
+        st.kind = 3;
+        plan_cl_level(st.cl, ly, jl - 1, Hl[jl - 1], Wl[jl - 1], true, 0.5f);
+        st.smem_bytes = 0;
+        st.xin_off = (jl == 1) ? -1 : poff[jl - 1];
+        st.rin_off = roff[jl];
+        st.rout_off = (jl == 1) ? -1 : roff[jl - 1];
+        ch.stages.push_back(st);
+      }
       return ch;
     }
   }
