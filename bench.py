@@ -681,6 +681,83 @@ def run_model(args):
     return 0
 
 
+# ---------------------------------------------------------------------------
+# Single-layer workloads (`--workload wtconv1d | segmentation | train`): the other BASELINE layer
+# configurations and the layer-set training step as lines of their own (1 GPU; also the small
+# cases the profiler captures run, with --batch)
+# ---------------------------------------------------------------------------
+def run_single(args):
+    import wtconv_b200
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the WTConv kernels have no CPU path")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    timer = Timer(dev, None)
+    peak, peak_kind = load_peaks()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    kind = args.workload
+    if kind == "wtconv1d":
+        B = args.batch if args.batch != 128 else 512
+        C, L, N = 64, 4, args.length
+        m = load_state(wtconv_b200.WTConv1d(C, C, kernel_size=KSIZE, wt_levels=L), synthetic_state(C, L, 500, ndim=1)).to(dev).eval()
+        nb = max(2, min(4, int(1.2e9 / (B * C * N * 4))))
+        xs = [torch.randn(B, C, N, device=dev) for _ in range(nb)]
+        nbytes = 2 * B * C * N * 4 + param_bytes(C, L, 4, ndim=1)
+        name, dtype, launches = f"WTConv1d(64,64,5,wt_levels=4) on ({B},64,{N}) fp32", "f32", 1
+        metric = "wtconv1d_layer_algorithmic_GBps"
+    elif kind == "segmentation":
+        B = args.batch if args.batch != 128 else 2
+        C, L, H = 256, 5, 512
+        m = load_state(wtconv_b200.WTConv2d(C, C, kernel_size=KSIZE, wt_levels=L), synthetic_state(C, L, 400)).to(dev).to(torch.bfloat16).eval()
+        xs = [torch.randn(B, C, H, H, device=dev, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last) for _ in range(2)]
+        nbytes = layer_bytes(B, C, H, L, 2)
+        name, dtype, launches = f"WTConv2d(256,256,5,wt_levels=5) on ({B},256,512,512) bf16 channels-last", "bf16", layer_launches(B, C, H, L)
+        metric = "wtconv2d_segmentation_layer_algorithmic_GBps"
+    else:   # train: forward + backward (input and parameter gradients) of the four stage layers, bf16
+        B = args.batch
+        layers = [l.train() for l in build_layers(dev)]
+        for l in layers:
+            for q in l.parameters():
+                q.requires_grad_(True)
+            l.wt_filter.requires_grad_(False)
+            l.iwt_filter.requires_grad_(False)
+        xs = [[torch.randn(B, C, H, H, device=dev, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+               for C, H, L in STAGES] for _ in range(2)]
+        gs = [torch.randn_like(x) for x in xs[0]]
+        nbytes = 3 * step_bytes(B)       # x, dL/dy read and dL/dx written on top of the forward's traffic, roughly
+        name, dtype, launches = f"layer set forward + backward at batch {B}, bf16 channels-last", "bf16", None
+        metric = "wtconv2d_layer_set_train_step_ms"
+
+    if kind == "train":
+        def step(i):
+            for l, x, g in zip(layers, xs[i % 2], gs):
+                l.zero_grad(set_to_none=True)
+                x.grad = None
+                l(x).backward(g)
+        per = []
+        for w in range(max(3, args.windows // 5)):
+            for i in range(args.warmup if w == 0 else 0):
+                step(i)
+            per.append(timer.window(step, max(2, args.steps // 4)))
+    else:
+        per = timer.run(lambda i: m(xs[i % len(xs)]), args.steps, args.warmup, max(3, args.windows // 5))
+    ms = statistics.median(per)
+    clocks = sampler.stop()
+    gbps = nbytes / (ms * 1e-3) / 1e9
+    line = {"metric": metric, "value": ms if kind == "train" else gbps, "unit": "ms" if kind == "train" else UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": kind != "train",
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": name},
+            "roofline": None if kind == "train" else {"bound": "hbm", "achieved": gbps, "peak": peak, "unit": "GB/s",
+                                                      "frac": gbps / peak, "traffic": None, "peak_source": f"of {peak_kind}"},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": None if launches is None else launches * args.steps * max(3, args.windows // 5),
+            "clocks": clocks}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     global BATCH, STAGES, WINDOWS
     ap = argparse.ArgumentParser()
@@ -691,14 +768,23 @@ def main():
     ap.add_argument("--batch", type=int, default=128, help="per-GPU batch (128 = the BASELINE workload; "
                     "smaller values are for profiler captures)")
     ap.add_argument("--stages", default="0,1,2,3", help="subset of the four stage layers (profiler captures)")
-    ap.add_argument("--workload", default="layers", choices=["layers", "model"],
-                    help="layers: the WTConv2d layer set (headline); model: WTConvNeXt-T images/sec")
+    ap.add_argument("--workload", default="layers", choices=["layers", "model", "wtconv1d", "segmentation", "train"],
+                    help="layers: the WTConv2d layer set (headline); model: WTConvNeXt-T images/sec; wtconv1d / "
+                         "segmentation: the 1-D and the 512x512 layer alone; train: forward + backward of the layer set")
+    ap.add_argument("--length", type=int, default=4096, help="signal length of --workload wtconv1d")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (profiler captures)")
     ap.add_argument("--windows", type=int, default=WINDOWS, help="timed windows of --steps steps (median reported)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.workload == "model":
         return run_model(args)
+    if args.workload in ("wtconv1d", "segmentation", "train"):
+        WINDOWS = max(1, args.windows)
+        args.windows = WINDOWS
+        if args.workload == "train":
+            BATCH = args.batch
+            STAGES = [STAGES[int(i)] for i in args.stages.split(",")]
+        return run_single(args)
     BATCH = args.batch
     WINDOWS = max(1, args.windows)
     STAGES = [STAGES[int(i)] for i in args.stages.split(",")]

@@ -94,7 +94,8 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   static bool done[kMaxDevices] = {false};
   cudaError_t e = allow_full_smem(kern, done);
   if (e != cudaSuccess) return e;
-  const dim3 grid((unsigned)(a.nby * a.nbx), (unsigned)a.ngroups, (unsigned)a.nslot_groups);
+  if (a.nby * a.nbx > 65535) return cudaErrorInvalidConfiguration;   // grid.y carries the band (planes beyond about 3500 x 3500)
+  const dim3 grid((unsigned)a.ngroups, (unsigned)(a.nby * a.nbx), (unsigned)a.nslot_groups);
   kern<<<grid, G::NT, smem, stream>>>(map, a);
   return cudaGetLastError();
   }

@@ -358,10 +358,11 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::s_bytes + G::w_bytes);
 
   const int tid = threadIdx.x;
-  // grid: x = band (column band fastest), y = channel group, z = slot group
-  const int band = blockIdx.x;
+  // grid: x = channel group (fastest: the CTAs that share the 128-byte lines of a pixel run together),
+  // y = band (column band fastest), z = slot group
+  const int band = blockIdx.y;
   const int bx = band % a.nbx, by = band / a.nbx;
-  const int c0 = blockIdx.y * kClGroup;
+  const int c0 = blockIdx.x * kClGroup;
   const int n0 = blockIdx.z * NS;
   const int i0 = by * NTY * kClRH, j0 = bx * NTX * kClCW;    // first sub-band position of the band
   const int X0 = 2 * (j0 - HS), Y0 = 2 * (i0 - HS);          // pixel frame origin (may be negative)
@@ -385,7 +386,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     // [set][tap][16 channels] fp32; set 0 = base (taps, bias), 1..4 = sub-bands of the level
     constexpr unsigned kSetBytes = (unsigned)(G::TAPS * kClGroup * sizeof(float));
     const int nset = 1 + 4 * a.nlevels;
-    const float* src = a.packed + a.cl_off + ((size_t)blockIdx.y * nset + (BASE ? 0 : 1 + 4 * a.level)) * (G::TAPS * kClGroup);
+    const float* src = a.packed + a.cl_off + ((size_t)blockIdx.x * nset + (BASE ? 0 : 1 + 4 * a.level)) * (G::TAPS * kClGroup);
     const unsigned bytes = (BASE ? 5u : 4u) * kSetBytes;
     cl_mbar_expect_tx(&bars[G::NBOX], bytes);
     cl_bulk_load(reinterpret_cast<unsigned char*>(Wsm) + (BASE ? 0u : kSetBytes), src, bytes, &bars[G::NBOX]);
@@ -700,8 +701,8 @@ __global__ void __launch_bounds__(256) wt2d_cl_lowpass_kernel(const __grid_const
 // (16-bit) or 256-byte (fp32) line per position, and the synthesis butterfly
 // (wavelet.py:70-75) is two xor-shuffles across the sub-band bits of the lane index.
 // ---------------------------------------------------------------------------
-constexpr int kClDeepSetPitch = (5 * 5 + 1) * kClGroup * 4 + 32;   // bytes between the staged tap sets of a level (K = 5):
-                                                                  // 32 past a multiple of 128, so the four sets read by a warp fall into different banks
+constexpr int kClDeepSetPitch = (5 * 5 + 1) * kClGroup * 4 + 64;   // bytes between the staged tap sets of a level (K = 5):
+                                                                  // 64 past a multiple of 128, so the two sets read by a half warp (64 bytes each) fall into different banks
 constexpr int kClDeepLevelBytes = (4 * kClDeepSetPitch + 127) / 128 * 128;
 
 #ifdef __CUDA_ARCH__

@@ -87,7 +87,7 @@ inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, 
   }
   off = (off + 127) / 128 * 128;
   a.woff = (int)off;
-  off += (long long)2 * (((4 * ((K * K + 1) * kClGroup * 4 + 32)) + 127) / 128 * 128);   // two buffers of four padded tap sets
+  off += (long long)2 * (((4 * ((K * K + 1) * kClGroup * 4 + 64)) + 127) / 128 * 128);   // two buffers of four padded tap sets
   off = (off + 127) / 128 * 128;
   a.bar_off = (int)off;
   off += 128;

@@ -380,6 +380,13 @@ inline int cl_config(int W) {
   return 0;
 }
 
+// Bands (CTAs per plane slot) of the level stage on an H x W plane; they travel in grid.y
+inline long long cl_bands(int H, int W) {
+  static const int rows[4] = {4 * kClRH, 7 * kClRH, 4 * kClRH, 2 * kClRH}, cols[4] = {7 * kClCW, 4 * kClCW, 2 * kClCW, 1 * kClCW};
+  const int cfg = cl_config(W);
+  return (long long)cdiv((H + 1) / 2, rows[cfg]) * cdiv((W + 1) / 2, cols[cfg]);
+}
+
 // Description of a channels-last level stage.  level 0 with the base path finishes the layer
 // (input x, output y); a deeper level reads the low-pass plane of the level above from scratch
 // (dense channels-last, the layer's type) and writes an fp32 reconstruction.
@@ -426,7 +433,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
   // Bottom of the pyramid: when the plane of some level q is small enough for the
   // register-resident kernel (channels-last tensors, every remaining level), that kernel
   // takes levels q+1..L; the CTA-tile stages above it cover levels 1..q only.
-  const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly);
+  const bool use_cl = tune.cl >= 0 && cl_stage_supported(ly) && cl_bands(ly.H, ly.W) <= 65535;
   // Channels-last tensors larger than 16 x 16 (smaller planes are faster in the register-level
   // kernels below): the sub-band pyramid kernel and a deep stage (whole
   // planes on chip) for the levels below the top one, then the level stage of the top level with
