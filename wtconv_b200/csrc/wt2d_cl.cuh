@@ -578,13 +578,14 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 #ifdef __CUDA_ARCH__
   const int P = (a.C + 1) / 2;
   const bool cpair = a.x_vec != 0;
-  for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < a.total; id += (long long)gridDim.x * blockDim.x) {
-    const int p = (int)(id % P);
-    long long t = id / P;
-    const int f = (int)(t % a.w2);
-    t /= a.w2;
-    const int k = (int)(t % a.h2);
-    const int n = (int)(t / a.h2);
+  // 32-bit index arithmetic (the launcher keeps the item count below 2^31)
+  for (unsigned id = blockIdx.x * blockDim.x + threadIdx.x; id < (unsigned)a.total; id += gridDim.x * blockDim.x) {
+    const int p = (int)(id % (unsigned)P);
+    unsigned t = id / (unsigned)P;
+    const int f = (int)(t % (unsigned)a.w2);
+    t /= (unsigned)a.w2;
+    const int k = (int)(t % (unsigned)a.h2);
+    const int n = (int)(t / (unsigned)a.h2);
     const int c = 2 * p;
     const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
     const bool both = (c + 1 < a.C);
@@ -639,13 +640,14 @@ __global__ void __launch_bounds__(256) wt2d_cl_lowpass_kernel(const __grid_const
   const int P = (a.C + 1) / 2;
   const bool cpair = a.x_vec != 0;
   const bool even_c = (a.C & 1) == 0;
-  for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < a.total; id += (long long)gridDim.x * blockDim.x) {
-    const int p = (int)(id % P);
-    long long t = id / P;
-    const int f = (int)(t % a.w2);
-    t /= a.w2;
-    const int k = (int)(t % a.h2);
-    const int n = (int)(t / a.h2);
+  // 32-bit index arithmetic (the launcher keeps the item count below 2^31)
+  for (unsigned id = blockIdx.x * blockDim.x + threadIdx.x; id < (unsigned)a.total; id += gridDim.x * blockDim.x) {
+    const int p = (int)(id % (unsigned)P);
+    unsigned t = id / (unsigned)P;
+    const int f = (int)(t % (unsigned)a.w2);
+    t /= (unsigned)a.w2;
+    const int k = (int)(t % (unsigned)a.h2);
+    const int n = (int)(t / (unsigned)a.h2);
     const int c = 2 * p;
     const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
     const bool both = (c + 1 < a.C);
@@ -728,11 +730,17 @@ __device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsign
 #pragma unroll
     for (int t = 0; t < K * K; ++t) wr[t] = w[t * kClLanes];
   }
-  const bool neg0 = (sbi & 1) != 0, neg1 = (sbi & 2) != 0;
+  // signs of the two butterfly stages for this lane: v' = partner + sign * v
+  const float2 sg0 = (sbi & 1) ? make_float2(-1.f, -1.f) : make_float2(1.f, 1.f);
+  const float2 sg1 = (sbi & 2) ? make_float2(-1.f, -1.f) : make_float2(1.f, 1.f);
+  const int dy = sbi & 1, dx = sbi >> 1;                       // pixel of the 2 x 2 block this lane ends up with
+  const bool chan_ok = c0 + 2 * cp < a.C, chan_pair = c0 + 2 * cp + 1 < a.C && (a.C & 1) == 0;
+  // tile coordinates advance with the tile index (no division in the loop)
+  const int per_slot = tyn * txn;
+  int slot = warp / per_slot, rem = warp - slot * per_slot;
+  int ty = rem / txn, tx = rem - ty * txn;
+  const int dslot = nwarp / per_slot, drem = nwarp - dslot * per_slot, dty = drem / txn, dtx = drem - dty * txn;
   for (int q = warp; q < ntile; q += nwarp) {      // warp-uniform bound: every lane takes part in the shuffles
-    const int slot = q / (tyn * txn);
-    const int rem = q - slot * (tyn * txn);
-    const int ty = rem / txn, tx = rem - ty * txn;
     const int gi = ty * RT, gj = tx * CT;
     float2 y[RT][CT];
 #pragma unroll
@@ -740,14 +748,13 @@ __device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsign
 #pragma unroll
       for (int jj = 0; jj < CT; ++jj) y[i][jj] = make_float2(0.f, 0.f);
     if (Rin && sbi == 0) {                         // the deeper reconstruction joins the low-pass result
-      const float* rb = Rin + (size_t)slot * a.rslot[j + 1] + 2 * cp;
+      const float* rb = Rin + (size_t)slot * a.rslot[j + 1] + (gi * wj + gj) * kClGroup + 2 * cp;
 #pragma unroll
       for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int jj = 0; jj < CT; ++jj)
           if (gi + i < hj && gj + jj < wj)
-            y[i][jj] = __fmul2_rn(*reinterpret_cast<const float2*>(rb + ((gi + i) * wj + gj + jj) * kClGroup),
-                                  make_float2(0.5f, 0.5f));
+            y[i][jj] = __fmul2_rn(*reinterpret_cast<const float2*>(rb + (i * wj + jj) * kClGroup), make_float2(0.5f, 0.5f));
     }
     const T* win = Sj + (size_t)slot * a.sslot[j] + ((size_t)gi * pitch + gj) * POS + sbi * kClGroup + 2 * cp;
 #pragma unroll
@@ -756,21 +763,34 @@ __device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsign
 #pragma unroll
       for (int c = 0; c < CT + K - 1; ++c) in[c] = ClPair<T>::load(win + (iy * pitch + c) * POS);
 #pragma unroll
-      for (int dy = 0; dy < K; ++dy) {
-        const int oy = iy - dy;
+      for (int ddy = 0; ddy < K; ++ddy) {
+        const int oy = iy - ddy;
         if (oy >= 0 && oy < RT) {
 #pragma unroll
-          for (int dx = 0; dx < K; ++dx)
+          for (int ddx = 0; ddx < K; ++ddx)
 #pragma unroll
-            for (int ox = 0; ox < CT; ++ox) y[oy][ox] = cl_fma2(in[ox + dx], wr[dy * K + dx], y[oy][ox]);
+            for (int ox = 0; ox < CT; ++ox) y[oy][ox] = cl_fma2(in[ox + ddx], wr[ddy * K + ddx], y[oy][ox]);
         }
       }
     }
     // synthesis: out(2i+dy, 2j+dx) = LL + (-1)^dy LH + (-1)^dx HL + (-1)^(dy+dx) HH.  Two butterfly
     // stages over the sub-band bits of the lane; afterwards the lane of "sub-band" k holds the
     // pixel with dy = k & 1, dx = k >> 1.
-    const int n = n0 + slot;
-    const int dy = sbi & 1, dx = sbi >> 1;
+    const int y0 = 2 * gi + dy, x0 = 2 * gj + dx;              // this lane's pixel of position (0, 0) of the tile
+    float* obase;
+    int rowstep, colstep;                                      // floats between the pixels of neighbouring positions
+    bool writes;
+    if (Rout) {
+      obase = Rout + (size_t)slot * a.rslot[j] + (y0 * wp + x0) * kClGroup + 2 * cp;
+      rowstep = 2 * wp * kClGroup; colstep = 2 * kClGroup;
+      writes = true;
+    } else {
+      const int n = n0 + slot;
+      obase = a.rout + (((size_t)n * hp + y0) * wp + x0) * a.C + c0 + 2 * cp;
+      rowstep = 2 * wp * a.C; colstep = 2 * a.C;
+      writes = n < a.B && chan_ok;
+    }
+    const bool vec = Rout || chan_pair;
 #pragma unroll
     for (int i = 0; i < RT; ++i)
 #pragma unroll
@@ -778,21 +798,20 @@ __device__ __forceinline__ void cl_deep_level(const ClDeepArgs& a, int j, unsign
         float2 v = y[i][jj], o;
         o.x = __shfl_xor_sync(kFull, v.x, 8);
         o.y = __shfl_xor_sync(kFull, v.y, 8);
-        v = neg0 ? cl_sub2(o, v) : cl_add2(v, o);
+        v = cl_fma2(v, sg0, o);
         o.x = __shfl_xor_sync(kFull, v.x, 16);
         o.y = __shfl_xor_sync(kFull, v.y, 16);
-        v = neg1 ? cl_sub2(o, v) : cl_add2(v, o);
-        const int yy = 2 * (gi + i) + dy, xx = 2 * (gj + jj) + dx;
-        if (yy < hp && xx < wp) {
-          if (Rout) {
-            *reinterpret_cast<float2*>(Rout + (size_t)slot * a.rslot[j] + (yy * wp + xx) * kClGroup + 2 * cp) = v;
-          } else if (n < a.B && c0 + 2 * cp < a.C) {
-            float* g = a.rout + (((size_t)n * hp + yy) * wp + xx) * a.C + c0 + 2 * cp;
-            if (c0 + 2 * cp + 1 < a.C && (a.C & 1) == 0) *reinterpret_cast<float2*>(g) = v;
-            else { g[0] = v.x; if (c0 + 2 * cp + 1 < a.C) g[1] = v.y; }
-          }
+        v = cl_fma2(v, sg1, o);
+        if (writes && y0 + 2 * i < hp && x0 + 2 * jj < wp) {
+          float* g = obase + i * rowstep + jj * colstep;
+          if (vec) *reinterpret_cast<float2*>(g) = v;
+          else { g[0] = v.x; if (c0 + 2 * cp + 1 < a.C) g[1] = v.y; }
         }
       }
+    // next tile of this warp
+    slot += dslot; ty += dty; tx += dtx;
+    if (tx >= txn) { tx -= txn; ++ty; }
+    if (ty >= tyn) { ty -= tyn; ++slot; }
   }
 }
 #endif
@@ -839,33 +858,32 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   bool ok = cl_mbar_wait(&bars[2], 0u);
 
-  // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j.  A warp owns a
-  // position; its lane (sub-band, channel pair) forms one sub-band of one channel pair.
-  {
-    const int lane = tid & 31, sbi = lane >> 3, cp = lane & (kClLanes - 1);
-    const float2 h = make_float2(0.5f, 0.5f);
-    const float2 s1 = (sbi & 2) ? make_float2(-1.f, -1.f) : make_float2(1.f, 1.f);      // a -+ b, c -+ d
-    const float2 s2 = (sbi & 1) ? make_float2(-0.5f, -0.5f) : make_float2(0.5f, 0.5f);   // +- the lower row
-    for (int j = 2; j <= a.nlev; ++j) {
-      const T* Sp = reinterpret_cast<const T*>(sm + a.soff[j - 1]);
-      T* Sj = reinterpret_cast<T*>(sm + a.soff[j]);
-      const int hj = a.h[j], wj = a.w[j], pp_ = a.spitch[j - 1], pj = a.spitch[j];
-      const int items = a.ns * hj * wj;
-      for (int it = tid >> 5; it < items; it += nthr >> 5) {
-        const int f = it % wj;
-        const int r = (it / wj) % hj;
-        const int slot = it / (wj * hj);
-        // positions (2r, 2f) .. (2r+1, 2f+1) of the low-pass band; beyond the plane the frame holds zeros
-        const T* p = Sp + (size_t)slot * a.sslot[j - 1] + ((size_t)(2 * r + HS) * pp_ + 2 * f + HS) * POS + 2 * cp;
-        const float2 va = ClPair<T>::load(p), vb = ClPair<T>::load(p + POS);
-        const float2 vc = ClPair<T>::load(p + (size_t)pp_ * POS), vd = ClPair<T>::load(p + (size_t)pp_ * POS + POS);
-        // the same arithmetic as cl_haar, for this lane's sub-band only
-        const float2 top = cl_fma2(vb, s1, va), bot = cl_fma2(vd, s1, vc);
-        const float2 v = cl_fma2(top, h, __fmul2_rn(bot, s2));
-        ClPair<T>::store(Sj + (size_t)slot * a.sslot[j] + ((size_t)(r + HS) * pj + f + HS) * POS + sbi * kClGroup + 2 * cp, v);
-      }
-      __syncthreads();
+  // ---- pass 2: analyses of the deeper levels, low-pass band of S_{j-1} -> S_j; a thread forms the
+  // four sub-bands of one channel pair at one position
+  for (int j = 2; j <= a.nlev; ++j) {
+    const T* Sp = reinterpret_cast<const T*>(sm + a.soff[j - 1]);
+    T* Sj = reinterpret_cast<T*>(sm + a.soff[j]);
+    const unsigned hj = a.h[j], wj = a.w[j];
+    const int pp_ = a.spitch[j - 1], pj = a.spitch[j];
+    const unsigned items = a.ns * hj * wj * kClLanes;
+    for (unsigned it = tid; it < items; it += nthr) {
+      const int cp = it & (kClLanes - 1);
+      const unsigned blk = it >> 3;
+      const int f = (int)(blk % wj);
+      const unsigned rs = blk / wj;
+      const int r = (int)(rs % hj);
+      const int slot = (int)(rs / hj);
+      // positions (2r, 2f) .. (2r+1, 2f+1) of the low-pass band; beyond the plane the frame holds zeros
+      const T* p = Sp + (size_t)slot * a.sslot[j - 1] + ((size_t)(2 * r + HS) * pp_ + 2 * f + HS) * POS + 2 * cp;
+      const float2 va = ClPair<T>::load(p), vb = ClPair<T>::load(p + POS);
+      const float2 vc = ClPair<T>::load(p + (size_t)pp_ * POS), vd = ClPair<T>::load(p + (size_t)pp_ * POS + POS);
+      float2 sb[4];
+      cl_haar(va, vb, vc, vd, sb);
+      T* d = Sj + (size_t)slot * a.sslot[j] + ((size_t)(r + HS) * pj + f + HS) * POS + 2 * cp;
+#pragma unroll
+      for (int s4 = 0; s4 < 4; ++s4) ClPair<T>::store(d + s4 * kClGroup, sb[s4]);
     }
+    __syncthreads();
   }
 
   // ---- pass 3: convolutions + synthesis, deepest level first; the tap sets of the next level are

@@ -365,6 +365,7 @@ inline bool plan_whole_plane(Plan2d& p, long long& smem, bool& good, const Layer
 // stride 1, every other stride and the base address multiples of 16 bytes.
 inline bool cl_stage_supported(const Layer2d& ly) {
   if (ly.K != 5 || ly.stride != 1 || ly.C < 8) return false;
+  if ((long long)ly.B * ly.C * ly.H * ly.W >= (1LL << 35)) return false;   // 32-bit item indices in the pyramid kernels
   if (ly.xs[1] != 1 || ly.ys[1] != 1) return false;
   if (ly.x_align < 16) return false;
   for (int i = 0; i < 4; ++i)
