@@ -77,6 +77,37 @@ def test_stage_layers_at_batch_128(stage, dtype):
     _check(y[idx].cpu(), x[idx], params, dtype)
 
 
+def test_odd_batch_with_two_slots_per_cta():
+    """Stage-2 shape at batch 129: the deep stage packs two samples per CTA, so its last CTA owns a
+    sample slot beyond the batch (its sub-band box is all out-of-bounds fill and nothing is stored)."""
+    dev = _cuda()
+    C, H, L = STAGES[1]
+    params = wtconv_torch.random_params(C, 5, L, seed=101)
+    x = torch.randn(129, C, H, H, generator=torch.Generator().manual_seed(77))
+    m = _module(2, C, L, params, torch.bfloat16, dev)
+    with torch.no_grad():
+        y = m(x.to(dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last))
+    assert torch.isfinite(y.float()).all()
+    idx = [0, 127, 128]
+    _check(y[idx].cpu(), x[idx], params, torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape,L", [((1, 16, 300, 261), 6), ((2, 8, 130, 257), 4), ((1, 32, 224, 224), 5), ((1, 24, 97, 140), 3)])
+def test_large_channels_last_planes(shape, L, dtype):
+    """Planes whose deeper sub-bands do not fit on chip: low-pass plane kernel, one level stage per
+    level, deep stage for the rest (odd sizes at every level, channel counts that do not fill a group)."""
+    dev = _cuda()
+    B, C, H, W = shape
+    params = wtconv_torch.random_params(C, 5, L, seed=H + L)
+    x = torch.randn(*shape, generator=torch.Generator().manual_seed(W))
+    m = _module(2, C, L, params, dtype, dev)
+    with torch.no_grad():
+        y = m(x.to(dev).to(dtype).contiguous(memory_format=torch.channels_last))
+    assert y.shape == x.shape and y.is_contiguous(memory_format=torch.channels_last)
+    _check(y.cpu(), x, params, dtype)
+
+
 @pytest.mark.parametrize("layout", ["cl", "nchw"])
 def test_segmentation_layer_512(layout):
     """BASELINE config 4: WTConv2d(256,256,5,wt_levels=5) on (2,256,512,512) bf16, both layouts; the
