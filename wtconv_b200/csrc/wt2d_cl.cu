@@ -11,6 +11,24 @@ namespace wt {
 
 namespace {
 
+// Launch with or without the programmatic-dependent-launch attribute (the kernel then calls
+// griddepcontrol.wait before it reads what the preceding kernel of the stream wrote)
+template <typename Kern, typename... Args>
+cudaError_t launch_maybe_dependent(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream, bool dependent,
+                                   const Args&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -88,6 +106,7 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   for (int i = 0; i < 4; ++i) { a.rs[i] = s.rs[i]; a.os[i] = s.os[i]; }
   a.out_vec = s.out_vec; a.rin_vec = s.rin_vec; a.rin_scale = s.rin_scale;
   a.status = status;
+  a.pdl = (s.pdl && rin) ? 1 : 0;
 
   auto kern = wt2d_cl_level_kernel<T, TO, K, NTY, NTX, NS, BASE, MAXREG>;
   constexpr size_t smem = G::smem_bytes;
@@ -96,8 +115,7 @@ cudaError_t launch_cfg(const ClStage& s, const void* x, const float* rin, void* 
   if (e != cudaSuccess) return e;
   if (a.nby * a.nbx > 65535) return cudaErrorInvalidConfiguration;   // grid.y carries the band (planes beyond about 3500 x 3500)
   const dim3 grid((unsigned)a.ngroups, (unsigned)(a.nby * a.nbx), (unsigned)a.nslot_groups);
-  kern<<<grid, G::NT, smem, stream>>>(map, a);
-  return cudaGetLastError();
+  return launch_maybe_dependent(kern, grid, G::NT, smem, stream, a.pdl != 0, map, a);
   }
 }
 
@@ -125,8 +143,7 @@ cudaError_t launch_deep_t(const ClDeepArgs& a0, const void* s2, const float* pac
   cudaError_t e = allow_full_smem(kern, done);
   if (e != cudaSuccess) return e;
   const dim3 grid((unsigned)cdiv(a.C, kClGroup), (unsigned)cdiv(a.B, a.ns));
-  kern<<<grid, kClDeepThreads, (size_t)a.smem_bytes, stream>>>(map, a);
-  return cudaGetLastError();
+  return launch_maybe_dependent(kern, grid, kClDeepThreads, (size_t)a.smem_bytes, stream, a.pdl != 0, map, a);
 }
 
 template <typename T>

@@ -67,6 +67,7 @@ struct ClArgs {
   int rin_vec;             // 1: channel pairs of rin may be loaded as one 8-byte word
   float rin_scale;         // factor applied to rin: 1/2 for a reconstruction at the reference's scale
   int* status;             // device word that receives a nonzero code when a wait gives up
+  int pdl;                 // 1: launched as a programmatic dependent of the kernel that writes rin
 };
 
 // ---------------------------------------------------------------------------
@@ -108,6 +109,13 @@ __device__ __forceinline__ void cl_tma_load4(void* dst, const CUtensorMap* map, 
       ::"r"(cl_smem_addr(dst)), "l"(map), "r"(cl_smem_addr(bar)), "r"(c), "r"(x), "r"(y), "r"(n)
       : "memory");
 }
+
+// Programmatic dependent launch: the next kernel of the stream may be scheduled once every CTA of
+// this grid has got here (it still waits for this grid's completion before it reads its results)
+__device__ __forceinline__ void cl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// ... and the other side: blocks until the preceding grid of the stream has completed and its
+// writes are visible (a no-op for a kernel that was launched without the attribute)
+__device__ __forceinline__ void cl_wait_for_producer() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // 5-D tiled TMA load (channel, sub-band, column, row, sample) -> shared memory, completing on `bar`
 __device__ __forceinline__ void cl_tma_load5(void* dst, const CUtensorMap* map, void* bar, int c, int sb, int x, int y, int n) {
@@ -358,6 +366,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + G::s_bytes + G::w_bytes);
 
   const int tid = threadIdx.x;
+  cl_launch_dependents();
   // grid: x = channel group (fastest: the CTAs that share the 128-byte lines of a pixel run together),
   // y = band (column band fastest), z = slot group
   const int band = blockIdx.y;
@@ -461,7 +470,9 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   const bool pair = (c + 1 < a.C);
   if (!live) return;
 
-  // deeper reconstruction (wtconv2d.py:71), requested before the convolutions
+  // deeper reconstruction (wtconv2d.py:71), requested before the convolutions; its producer is the
+  // preceding kernel of the stream, which may still be running when this one was launched early
+  if (a.pdl) cl_wait_for_producer();
   float2 rin[kClRH][kClCW];
 #pragma unroll
   for (int i = 0; i < kClRH; ++i)
@@ -576,6 +587,7 @@ struct ClPyramidArgs {
 template <typename T>
 __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_constant__ ClPyramidArgs a) {
 #ifdef __CUDA_ARCH__
+  cl_launch_dependents();
   const int P = (a.C + 1) / 2;
   const bool cpair = a.x_vec != 0;
   // 32-bit index arithmetic (the launcher keeps the item count below 2^31)
@@ -843,14 +855,17 @@ wt2d_cl_deep_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                    wsrc + (size_t)(1 + 4 * (a.lvl0 + j) + sb) * (TAPS * kClGroup), kSetBytes, &bars[buf]);
   };
 
+  cl_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < 3; ++s) cl_mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    load_taps(a.nlev, 0);                            // deepest level first
+    // the sub-bands come from the preceding kernel of the stream (this one may have been launched early)
+    if (a.pdl) cl_wait_for_producer();
     // S_1 of every slot: one box over the four sub-bands, starting HS positions outside the plane
     cl_mbar_expect_tx(&bars[2], (unsigned)(a.ns * a.sslot[1] * (int)sizeof(T)));
     for (int sl = 0; sl < a.ns; ++sl)
       cl_tma_load5(sm + a.soff[1] + (size_t)sl * a.sslot[1] * sizeof(T), &xmap, &bars[2], c0, 0, -HS, -HS, n0 + sl);
-    load_taps(a.nlev, 0);                            // deepest level first
   }
   // zero borders (and overhang) of the deeper frames (S_1 is filled whole by the TMA boxes)
   for (int i = tid; i < a.zero_bytes / 16; i += nthr)

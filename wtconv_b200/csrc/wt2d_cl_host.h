@@ -25,6 +25,8 @@ struct ClStage {
   long long os[4];       // output strides in elements: n, c (= 1), h, w
   int out_vec, rin_vec, x_vec;  // channel pairs of the output / reconstruction / input may be moved as one word
   float rin_scale;       // factor applied to the deeper reconstruction (1/2: it is at the reference's scale)
+  int pdl;               // 1: the kernel that writes the reconstruction is the preceding launch of the stream:
+                         // launch as its programmatic dependent (starts while that kernel drains)
 };
 
 // dtype: 0 fp32, 1 bf16, 2 fp16 (type of the input plane set; the layer output has the same type)
@@ -55,13 +57,14 @@ struct ClDeepArgs {
   long long cl_off;               // floats from `packed` to the channels-last parameter copy
   float* rout;                    // (B, h[0], w[0], C) fp32
   int* status;
+  int pdl;                        // 1: launched as a programmatic dependent of the pyramid kernel
 };
 
 // Fills the geometry of the deep stage for `ns` slots per CTA; returns the shared memory it
 // needs in bytes, or -1 when the plane set cannot be handled.
 inline long long plan_cl_deep(ClDeepArgs& a, int B, int C, int H, int W, int K, int L, int elem_size, int ns) {
   const int HS = K / 2;
-  a.B = B; a.C = C; a.H = H; a.W = W; a.ns = ns; a.nlevels = L; a.lvl0 = 0;
+  a.B = B; a.C = C; a.H = H; a.W = W; a.ns = ns; a.nlevels = L; a.lvl0 = 0; a.pdl = 0;
   a.nlev = L - 1;
   if (a.nlev < 1 || a.nlev > kClDeepMaxLev || ns > 64) return -1;
   a.h[0] = (H + 1) / 2; a.w[0] = (W + 1) / 2;

@@ -413,6 +413,7 @@ inline void plan_cl_level(ClStage& s, const Layer2d& ly, int level, int H, int W
     s.rin_vec = 0;
   }
   s.rin_scale = rin_scale;
+  s.pdl = 0;
   s.x_vec = final_stage ? ((ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0)
                         : ((ly.C % 2 == 0) ? 1 : 0);
   if (final_stage) {
@@ -501,6 +502,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
         deep.deep.cl_off = cl_param_offset(ly.C, ly.K, ly.L);
         deep.deep.nlevels = ly.L;
         deep.deep.lvl0 = nl - 1;
+        deep.deep.pdl = 1;                                     // the pyramid kernel is the launch before it
         deep.xin_off = soff; deep.rin_off = -1; deep.rout_off = roff[nl];
         deep.smem_bytes = deep.deep.smem_bytes;
         ch.stages.push_back(deep);
@@ -509,6 +511,7 @@ inline Chain2d plan_layer(const Layer2d& ly, const Tuning2d& tune = Tuning2d()) 
         Stage2d st;
         st.kind = 3;
         plan_cl_level(st.cl, ly, jl - 1, Hl[jl - 1], Wl[jl - 1], true, 0.5f);
+        st.cl.pdl = 1;                                         // its reconstruction comes from the launch before it
         st.smem_bytes = 0;
         st.xin_off = (jl == 1) ? -1 : poff[jl - 1];
         st.rin_off = roff[jl];
