@@ -3,13 +3,18 @@
  *
  * Plain C, no torch types: raw device pointers, sizes, element strides and a
  * CUDA stream handle passed as void*.  The library never allocates or frees
- * device memory in the entry points below, never synchronises the stream and
- * never throws: every call returns a status (0 = ok, <0 = rejected argument or
- * un-built variant, >0 = a cudaError_t from the launch).  All kernels run on
- * the CURRENT device of the calling thread, on the given stream; the entry
- * points keep no global mutable state, so they may be called concurrently from
- * several host threads (the reference's validate.py:263 nn.DataParallel path
- * does that).
+ * device memory in the entry points below, never synchronises the stream
+ * (wtconv_device_status excepted: it exists to do so) and never throws: every
+ * call returns a status (0 = ok, <0 = rejected argument or un-built variant,
+ * >0 = a cudaError_t from the launch).  All kernels run on the CURRENT device
+ * of the calling thread, on the given stream.  The only state the library
+ * keeps between calls is host-side and guarded by a mutex or read and written
+ * atomically (a cache of launch plans keyed by the problem description,
+ * per-device "kernel attribute set" flags) plus, on each device, the scratch
+ * array of wtconv2d_forward_noalloc and the status word of
+ * wtconv_device_status; the entry points may therefore be called concurrently
+ * from several host threads (the reference's validate.py:263 nn.DataParallel
+ * path does that).
  *
  * What each entry point replaces in the reference project (paths inside the
  * reference repository) is given beside its declaration.

@@ -108,9 +108,11 @@ inline cudaError_t allow_full_smem(Kern kern, bool (&done)[kMaxDevices]) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  if (done[dev]) return cudaSuccess;
+  // the flag is read and written atomically: host threads may launch the same kernel concurrently
+  // (setting the attribute twice is harmless)
+  if (__atomic_load_n(&done[dev], __ATOMIC_ACQUIRE)) return cudaSuccess;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
-  if (e == cudaSuccess) done[dev] = true;
+  if (e == cudaSuccess) __atomic_store_n(&done[dev], true, __ATOMIC_RELEASE);
   return e;
 }
 #endif
