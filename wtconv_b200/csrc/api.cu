@@ -421,8 +421,14 @@ int wtconv2d_forward(const void* x, void* y, const float* packed, void* workspac
       case 6: {   // low-pass planes one and two levels below it
         const long long dense[4] = {(long long)sg.cl.H * sg.cl.W * ly.C, 1, (long long)sg.cl.W * ly.C, ly.C};
         const long long* s = from_x ? ly.xs : dense;
-        const int xv = from_x ? ((ly.x_align >= 2 * ly.elem_size && (ly.xs[0] % 2) == 0 && (ly.xs[2] % 2) == 0 && (ly.xs[3] % 2) == 0) ? 1 : 0)
-                              : ((ly.C % 2 == 0) ? 1 : 0);
+        // 2: four channels of a pixel may be moved as one 8- / 16-byte access, 1: pairs as one word, 0: neither
+        int xv;
+        if (from_x) {
+          auto mult = [&](int m) { return ly.x_align >= m * ly.elem_size && (ly.xs[0] % m) == 0 && (ly.xs[2] % m) == 0 && (ly.xs[3] % m) == 0; };
+          xv = mult(4) ? 2 : (mult(2) ? 1 : 0);
+        } else {
+          xv = (ly.C % 4 == 0) ? 2 : ((ly.C % 2 == 0) ? 1 : 0);
+        }
         if (sg.kind == 5) e = launch_cl_pyramid(dtype, xin, s, xv, ly.B, ly.C, sg.cl.H, sg.cl.W, rout, cs);
         else e = launch_cl_lowpass(dtype, xin, s, xv, ly.B, ly.C, sg.cl.H, sg.cl.W, rout,
                                    sg.rin_off < 0 ? nullptr : static_cast<void*>(ws + sg.rin_off), cs);

@@ -156,11 +156,14 @@ cudaError_t launch_pyramid_t(const void* x, const long long* xs, int x_vec, int 
   a.B = B; a.C = C; a.H = H; a.W = W;
   a.h2 = ((H + 1) / 2 + 1) / 2; a.w2 = ((W + 1) / 2 + 1) / 2;
   a.s2 = s2;
-  a.total = (long long)B * a.h2 * a.w2 * ((C + 1) / 2);
+  // four channels per thread when the pixels allow 8- / 16-byte accesses (x_vec = 2), else pairs
+  const bool quad = x_vec >= 2 && C % 4 == 0;
+  a.total = (long long)B * a.h2 * a.w2 * (quad ? C / 4 : (C + 1) / 2);
   if (a.total >= (1LL << 31) - 148 * 64 * 256) return cudaErrorInvalidConfiguration;   // 32-bit item index in the kernel
   const long long want = (a.total + 255) / 256;
   const int blocks = (int)(want > 148 * 64 ? 148 * 64 : want);
-  wt2d_cl_pyramid_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  if (quad) wt2d_cl_pyramid4_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  else wt2d_cl_pyramid_kernel<T><<<blocks, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
 
@@ -175,11 +178,13 @@ cudaError_t launch_lowpass_t(const void* x, const long long* xs, int x_vec, int 
   a.h1 = (H + 1) / 2; a.w1 = (W + 1) / 2;
   a.h2 = (a.h1 + 1) / 2; a.w2 = (a.w1 + 1) / 2;
   a.p1 = p1; a.p2 = p2;
-  a.total = (long long)B * a.h2 * a.w2 * ((C + 1) / 2);
+  const bool quad = x_vec >= 2 && C % 4 == 0;
+  a.total = (long long)B * a.h2 * a.w2 * (quad ? C / 4 : (C + 1) / 2);
   if (a.total >= (1LL << 31) - 148 * 64 * 256) return cudaErrorInvalidConfiguration;   // 32-bit item index in the kernel
   const long long want = (a.total + 255) / 256;
   const int blocks = (int)(want > 148 * 64 ? 148 * 64 : want);
-  wt2d_cl_lowpass_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  if (quad) wt2d_cl_lowpass4_kernel<T><<<blocks, 256, 0, stream>>>(a);
+  else wt2d_cl_lowpass_kernel<T><<<blocks, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -220,6 +220,42 @@ template <> struct ClPair<__half> {
     *reinterpret_cast<__half2*>(p) = __float22half2_rn(v);
   }
 };
+
+// Four consecutive channels of a pixel as one 8-byte (16-bit types) or 16-byte (fp32) access; the
+// address must be aligned to the access.  The two channel pairs come back as ClPair raw values.
+template <typename T> struct ClQuad;
+template <> struct ClQuad<float> {
+  static __device__ __forceinline__ void load(const float* p, bool valid, float2& a, float2& b) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid) v = __ldg(reinterpret_cast<const float4*>(p));
+    a = make_float2(v.x, v.y); b = make_float2(v.z, v.w);
+  }
+  static __device__ __forceinline__ void store(float* p, float2 a, float2 b) {
+    *reinterpret_cast<float4*>(p) = make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+template <> struct ClQuad<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, bool valid, unsigned& a, unsigned& b) {
+    uint2 v = make_uint2(0u, 0u);
+    if (valid) v = __ldg(reinterpret_cast<const uint2*>(p));
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 a, float2 b) {
+    const __nv_bfloat162 ha = __float22bfloat162_rn(a), hb = __float22bfloat162_rn(b);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&ha), *reinterpret_cast<const unsigned*>(&hb));
+  }
+};
+template <> struct ClQuad<__half> {
+  static __device__ __forceinline__ void load(const __half* p, bool valid, unsigned& a, unsigned& b) {
+    uint2 v = make_uint2(0u, 0u);
+    if (valid) v = __ldg(reinterpret_cast<const uint2*>(p));
+    a = v.x; b = v.y;
+  }
+  static __device__ __forceinline__ void store(__half* p, float2 a, float2 b) {
+    const __half2 ha = __float22half2_rn(a), hb = __float22half2_rn(b);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&ha), *reinterpret_cast<const unsigned*>(&hb));
+  }
+};
 #endif
 
 // Compile-time geometry of one kernel configuration (T: type of the input plane set).  The
@@ -577,7 +613,7 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
 struct ClPyramidArgs {
   const void* x;
   long long xs[4];      // strides in elements: n, c (= 1), h, w
-  int x_vec;            // 1: channel pairs may be loaded as one word
+  int x_vec;            // 1: channel pairs may be loaded as one word; 2: four channels as one 8- / 16-byte access
   int B, C, H, W;
   int h2, w2;           // size of the second level's sub-bands: ceil(ceil(H/2)/2), ...
   void* s2;             // (B, h2, w2, 4, C)
@@ -628,6 +664,53 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 #endif
 }
 
+// The same with four channels per thread (channel counts that are multiples of four on tensors
+// whose pixels start on 16-byte boundaries -- every tensor the channels-last chains accept): half
+// the index arithmetic and half the memory instructions per byte.
+template <typename T>
+__global__ void __launch_bounds__(256) wt2d_cl_pyramid4_kernel(const __grid_constant__ ClPyramidArgs a) {
+#ifdef __CUDA_ARCH__
+  typedef typename ClPair<T>::raw_t raw_t;
+  cl_launch_dependents();
+  const unsigned Q = (unsigned)a.C / 4u;
+  for (unsigned id = blockIdx.x * blockDim.x + threadIdx.x; id < (unsigned)a.total; id += gridDim.x * blockDim.x) {
+    const int c = 4 * (int)(id % Q);
+    unsigned t = id / Q;
+    const int f = (int)(t % (unsigned)a.w2);
+    t /= (unsigned)a.w2;
+    const int k = (int)(t % (unsigned)a.h2);
+    const int n = (int)(t / (unsigned)a.h2);
+    const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
+    float2 l[2][2][2];                          // [pair][block row][block column]
+#pragma unroll
+    for (int by = 0; by < 2; ++by)
+#pragma unroll
+      for (int bx = 0; bx < 2; ++bx) {
+        raw_t r[2][2][2];                       // [pair][row][column] of the 2 x 2 pixel block
+#pragma unroll
+        for (int yy = 0; yy < 2; ++yy)
+#pragma unroll
+          for (int xx = 0; xx < 2; ++xx) {
+            const int py = 2 * by + yy, px = 2 * bx + xx;
+            ClQuad<T>::load(p0 + (long long)py * a.xs[2] + (long long)px * a.xs[3], 4 * k + py < a.H && 4 * f + px < a.W,
+                            r[0][yy][xx], r[1][yy][xx]);
+          }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          l[h][by][bx] = __fmul2_rn(cl_add2(cl_add2(ClPair<T>::widen(r[h][0][0]), ClPair<T>::widen(r[h][0][1])),
+                                            cl_add2(ClPair<T>::widen(r[h][1][0]), ClPair<T>::widen(r[h][1][1]))),
+                                    make_float2(0.5f, 0.5f));
+      }
+    float2 sa[4], sb[4];
+    cl_haar(l[0][0][0], l[0][0][1], l[0][1][0], l[0][1][1], sa);
+    cl_haar(l[1][0][0], l[1][0][1], l[1][1][0], l[1][1][1], sb);
+    T* d = static_cast<T*>(a.s2) + (((size_t)n * a.h2 + k) * a.w2 + f) * 4 * a.C + c;
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4) ClQuad<T>::store(d + (size_t)s4 * a.C, sa[s4], sb[s4]);
+  }
+#endif
+}
+
 // ---------------------------------------------------------------------------
 // Low-pass planes for the level stages below the top one (large planes only): a plane set
 // (the layer input, or a low-pass plane set written by an earlier launch of this kernel) ->
@@ -638,7 +721,7 @@ __global__ void __launch_bounds__(256) wt2d_cl_pyramid_kernel(const __grid_const
 struct ClLowpassArgs {
   const void* x;
   long long xs[4];      // strides in elements: n, c (= 1), h, w
-  int x_vec;            // 1: channel pairs may be loaded as one word
+  int x_vec;            // 1: channel pairs may be loaded as one word; 2: four channels as one 8- / 16-byte access
   int B, C, H, W;
   int h1, w1, h2, w2;   // sizes one and two levels down
   void* p1;             // (B, h1, w1, C)
@@ -689,6 +772,53 @@ __global__ void __launch_bounds__(256) wt2d_cl_lowpass_kernel(const __grid_const
       T* d = static_cast<T*>(a.p2) + (((size_t)n * a.h2 + k) * a.w2 + f) * a.C + c;
       if (both && even_c) ClPair<T>::store(d, ll);
       else { d[0] = Elem<T>::from_f(ll.x); if (both) d[1] = Elem<T>::from_f(ll.y); }
+    }
+  }
+#endif
+}
+
+// Four channels per thread (see wt2d_cl_pyramid4_kernel)
+template <typename T>
+__global__ void __launch_bounds__(256) wt2d_cl_lowpass4_kernel(const __grid_constant__ ClLowpassArgs a) {
+#ifdef __CUDA_ARCH__
+  typedef typename ClPair<T>::raw_t raw_t;
+  const unsigned Q = (unsigned)a.C / 4u;
+  for (unsigned id = blockIdx.x * blockDim.x + threadIdx.x; id < (unsigned)a.total; id += gridDim.x * blockDim.x) {
+    const int c = 4 * (int)(id % Q);
+    unsigned t = id / Q;
+    const int f = (int)(t % (unsigned)a.w2);
+    t /= (unsigned)a.w2;
+    const int k = (int)(t % (unsigned)a.h2);
+    const int n = (int)(t / (unsigned)a.h2);
+    const T* p0 = static_cast<const T*>(a.x) + (long long)n * a.xs[0] + (long long)(4 * k) * a.xs[2] + (long long)(4 * f) * a.xs[3] + c;
+    float2 l[2][2][2];
+#pragma unroll
+    for (int by = 0; by < 2; ++by)
+#pragma unroll
+      for (int bx = 0; bx < 2; ++bx) {
+        raw_t r[2][2][2];
+#pragma unroll
+        for (int yy = 0; yy < 2; ++yy)
+#pragma unroll
+          for (int xx = 0; xx < 2; ++xx) {
+            const int py = 2 * by + yy, px = 2 * bx + xx;
+            ClQuad<T>::load(p0 + (long long)py * a.xs[2] + (long long)px * a.xs[3], 4 * k + py < a.H && 4 * f + px < a.W,
+                            r[0][yy][xx], r[1][yy][xx]);
+          }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          l[h][by][bx] = __fmul2_rn(cl_add2(cl_add2(ClPair<T>::widen(r[h][0][0]), ClPair<T>::widen(r[h][0][1])),
+                                            cl_add2(ClPair<T>::widen(r[h][1][0]), ClPair<T>::widen(r[h][1][1]))),
+                                    make_float2(0.5f, 0.5f));
+        const int y1 = 2 * k + by, x1 = 2 * f + bx;
+        if (y1 < a.h1 && x1 < a.w1)
+          ClQuad<T>::store(static_cast<T*>(a.p1) + (((size_t)n * a.h1 + y1) * a.w1 + x1) * a.C + c, l[0][by][bx], l[1][by][bx]);
+      }
+    if (a.p2) {
+      const float2 h2 = make_float2(0.5f, 0.5f);
+      const float2 la = __fmul2_rn(cl_add2(cl_add2(l[0][0][0], l[0][0][1]), cl_add2(l[0][1][0], l[0][1][1])), h2);
+      const float2 lb = __fmul2_rn(cl_add2(cl_add2(l[1][0][0], l[1][0][1]), cl_add2(l[1][1][0], l[1][1][1])), h2);
+      ClQuad<T>::store(static_cast<T*>(a.p2) + (((size_t)n * a.h2 + k) * a.w2 + f) * a.C + c, la, lb);
     }
   }
 #endif
