@@ -156,6 +156,11 @@ template <typename T> struct ClPair;
 template <> struct ClPair<float> {
   typedef float2 raw_t;
   static __device__ __forceinline__ raw_t load_raw(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  // two neighbouring pairs (four channels) with one 16-byte access
+  static __device__ __forceinline__ void load_raw2(const float* p, raw_t& a, raw_t& b) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    a = make_float2(v.x, v.y); b = make_float2(v.z, v.w);
+  }
   static __device__ __forceinline__ float2 widen(raw_t r) { return r; }
   static __device__ __forceinline__ void store_raw(float* p, raw_t r) { *reinterpret_cast<float2*>(p) = r; }
   // channel pair from global memory; `both`: the second channel exists
@@ -173,6 +178,11 @@ template <> struct ClPair<float> {
 template <> struct ClPair<__nv_bfloat16> {
   typedef unsigned raw_t;
   static __device__ __forceinline__ raw_t load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned*>(p); }
+  // two neighbouring pairs (four channels) with one 8-byte access
+  static __device__ __forceinline__ void load_raw2(const __nv_bfloat16* p, raw_t& a, raw_t& b) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    a = v.x; b = v.y;
+  }
   // bf16 -> fp32 is a move of the 16 bits into the upper half: two byte permutes (integer pipe).
   // Written as prmt so that the compiler does not turn shift/mask into conversion instructions,
   // which issue at a fraction of the integer rate.
@@ -202,6 +212,10 @@ template <> struct ClPair<__nv_bfloat16> {
 template <> struct ClPair<__half> {
   typedef unsigned raw_t;
   static __device__ __forceinline__ raw_t load_raw(const __half* p) { return *reinterpret_cast<const unsigned*>(p); }
+  static __device__ __forceinline__ void load_raw2(const __half* p, raw_t& a, raw_t& b) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    a = v.x; b = v.y;
+  }
   static __device__ __forceinline__ float2 widen(raw_t u) { return __half22float2(*reinterpret_cast<const __half2*>(&u)); }
   static __device__ __forceinline__ void store_raw(__half* p, raw_t r) { *reinterpret_cast<unsigned*>(p) = r; }
   static __device__ __forceinline__ raw_t load_global(const __half* p, bool valid, bool vec, bool both) {
@@ -444,49 +458,53 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   // are its sub-band rows written -- they cover frame rows of this and of later batches only (a
   // sub-band row takes at least the bytes of its two pixel rows and both arrays start at the same
   // address), and batches run last rows first.  16-bit frames fit the registers in one batch.
+  // A block item is four channels (two pairs) of one position: 8- / 16-byte shared-memory accesses.
   constexpr int NB = G::NB, RB = SR / NB;
-  constexpr int BITEMS = NS * RB * SC * kClLanes;
+  constexpr int QL = kClLanes / 2;                     // items per position
+  constexpr int BITEMS = NS * RB * SC * QL;
   constexpr int NIT = (BITEMS + G::NT - 1) / G::NT;
   bool ok = true;
 #pragma unroll 1
   for (int bt = NB - 1; bt >= 0; --bt) {
     const int k0 = bt * RB;
     for (int b = (2 * k0) / G::BOXR; b <= (2 * (k0 + RB) - 1) / G::BOXR; ++b) ok = cl_mbar_wait(&bars[b], 0u) && ok;
-    raw_t px[NIT][4];
+    raw_t px[NIT][4][2];
 #pragma unroll
     for (int j = 0; j < NIT; ++j) {
       const int it = tid + j * G::NT;
       if (it >= BITEMS) continue;
-      const int cpj = it & (kClLanes - 1);
-      const int blk = it >> 3;
+      const int cq = it & (QL - 1);
+      const int blk = it / QL;
       const int f = blk % SC;
       const int t = blk / SC;
       const int k = k0 + t % RB;
       const int slot = t / RB;
-      const T* p = reinterpret_cast<const T*>(S + (size_t)slot * G::SLOT_S) + ((size_t)(2 * k) * XC + 2 * f) * kClGroup + 2 * cpj;
-      px[j][0] = ClPair<T>::load_raw(p);
-      px[j][1] = ClPair<T>::load_raw(p + kClGroup);
-      px[j][2] = ClPair<T>::load_raw(p + XC * kClGroup);
-      px[j][3] = ClPair<T>::load_raw(p + XC * kClGroup + kClGroup);
+      const T* p = reinterpret_cast<const T*>(S + (size_t)slot * G::SLOT_S) + ((size_t)(2 * k) * XC + 2 * f) * kClGroup + 4 * cq;
+      ClPair<T>::load_raw2(p, px[j][0][0], px[j][0][1]);
+      ClPair<T>::load_raw2(p + kClGroup, px[j][1][0], px[j][1][1]);
+      ClPair<T>::load_raw2(p + XC * kClGroup, px[j][2][0], px[j][2][1]);
+      ClPair<T>::load_raw2(p + XC * kClGroup + kClGroup, px[j][3][0], px[j][3][1]);
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < NIT; ++j) {
       const int it = tid + j * G::NT;
       if (it >= BITEMS) continue;
-      const int cpj = it & (kClLanes - 1);
-      const int blk = it >> 3;
+      const int cq = it & (QL - 1);
+      const int blk = it / QL;
       const int f = blk % SC;
       const int t = blk / SC;
       const int k = k0 + t % RB;
       const int slot = t / RB;
-      float2 sb[4];
-      cl_haar(ClPair<T>::widen(px[j][0]), ClPair<T>::widen(px[j][1]), ClPair<T>::widen(px[j][2]), ClPair<T>::widen(px[j][3]), sb);
+      float2 sa[4], sb[4];
+      cl_haar(ClPair<T>::widen(px[j][0][0]), ClPair<T>::widen(px[j][1][0]), ClPair<T>::widen(px[j][2][0]), ClPair<T>::widen(px[j][3][0]), sa);
+      cl_haar(ClPair<T>::widen(px[j][0][1]), ClPair<T>::widen(px[j][1][1]), ClPair<T>::widen(px[j][2][1]), ClPair<T>::widen(px[j][3][1]), sb);
       const int rot = ((f >> 2) + NTX * (k >> 1)) & (SL - 1);
       const int fs = (f & ~(SL - 1)) + ((f + rot) & (SL - 1));
-      float* d = S + (size_t)slot * G::SLOT_S + (size_t)k * G::ROWS + fs * kClGroup + 2 * cpj;
+      float* d = S + (size_t)slot * G::SLOT_S + (size_t)k * G::ROWS + fs * kClGroup + 4 * cq;
 #pragma unroll
-      for (int sbi = 0; sbi < 4; ++sbi) *reinterpret_cast<float2*>(d + sbi * G::SUBS) = sb[sbi];
+      for (int sbi = 0; sbi < 4; ++sbi)
+        *reinterpret_cast<float4*>(d + sbi * G::SUBS) = make_float4(sa[sbi].x, sa[sbi].y, sb[sbi].x, sb[sbi].y);
     }
   }
   ok = cl_mbar_wait(&bars[G::NBOX], 0u) && ok;        // tap sets
