@@ -524,30 +524,6 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   const bool pair = (c + 1 < a.C);
   if (!live) return;
 
-  // deeper reconstruction (wtconv2d.py:71), requested before the convolutions; its producer is the
-  // preceding kernel of the stream, which may still be running when this one was launched early
-  if (a.pdl) cl_wait_for_producer();
-  float2 rin[kClRH][kClCW];
-#pragma unroll
-  for (int i = 0; i < kClRH; ++i)
-#pragma unroll
-    for (int j = 0; j < kClCW; ++j) rin[i][j] = make_float2(0.f, 0.f);
-  if (a.rin) {
-    const float* rb = a.rin + (size_t)n * a.rs[0] + (size_t)c * a.rs[1];
-#pragma unroll
-    for (int i = 0; i < kClRH; ++i)
-#pragma unroll
-      for (int j = 0; j < kClCW; ++j) {
-        if (gi + i < a.Hh && gj + j < a.Wh) {
-          const float* rp = rb + (size_t)(gi + i) * a.rs[2] + (size_t)(gj + j) * a.rs[3];
-          if (a.rin_vec) rin[i][j] = __ldg(reinterpret_cast<const float2*>(rp));
-          else {
-            rin[i][j].x = __ldg(rp);
-            if (pair) rin[i][j].y = __ldg(rp + a.rs[1]);
-          }
-        }
-      }
-  }
   float2 acc[4][kClRH][kClCW];
 #pragma unroll
   for (int s = 0; s < 4; ++s)
@@ -561,8 +537,37 @@ wt2d_cl_level_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   const float* ps[SL];
 #pragma unroll
   for (int v = 0; v < SL; ++v) ps[v] = sbase + ((v + rot) & (SL - 1)) * kClGroup;
+  // Deeper reconstruction (wtconv2d.py:71).  Its producer is the preceding kernel of the stream, which
+  // may still be running when this one was launched early: the wait and the loads sit before the last
+  // of the four sub-band convolutions, so a CTA that started early has three of them behind it when
+  // it blocks, and the loads of the others are covered by the fourth.
+  float2 rin[kClRH][kClCW];
+#pragma unroll
+  for (int i = 0; i < kClRH; ++i)
+#pragma unroll
+    for (int j = 0; j < kClCW; ++j) rin[i][j] = make_float2(0.f, 0.f);
+  auto load_rin = [&]() {
+    if (a.pdl) cl_wait_for_producer();
+    if (a.rin) {
+      const float* rb = a.rin + (size_t)n * a.rs[0] + (size_t)c * a.rs[1];
+#pragma unroll
+      for (int i = 0; i < kClRH; ++i)
+#pragma unroll
+        for (int j = 0; j < kClCW; ++j) {
+          if (gi + i < a.Hh && gj + j < a.Wh) {
+            const float* rp = rb + (size_t)(gi + i) * a.rs[2] + (size_t)(gj + j) * a.rs[3];
+            if (a.rin_vec) rin[i][j] = __ldg(reinterpret_cast<const float2*>(rp));
+            else {
+              rin[i][j].x = __ldg(rp);
+              if (pair) rin[i][j].y = __ldg(rp + a.rs[1]);
+            }
+          }
+        }
+    }
+  };
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
+    if (s == 3) load_rin();
     const float* pss[SL];
 #pragma unroll
     for (int v = 0; v < SL; ++v) pss[v] = ps[v] + s * G::SUBS;
